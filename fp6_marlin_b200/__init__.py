@@ -1,0 +1,18 @@
+"""B200-native W(4&6)A16 GEMM: FP16 activations x mixed INT4 / FP6-E3M2 weights.
+
+The four callables of the reference's ``fp6_marlin`` module (``prepacking``, ``quantize``,
+``dequantize``, ``mul``) with the same signatures, plus helpers for the Blackwell weight layout.
+All compute runs in libfp6m.so (hand-written sm_100a CUDA + host C++) through a C ABI; importing
+this package fails if that library has not been built - there is no fallback path.
+"""
+from .api import (b200_sizes, dequantize, device_status, dump_operands, mul, pack_b200, prepacking,
+                  quantize, repack_from_reference, schedule, unpack_b200)
+from .quant import (W46Weight, decode_fp6, encode_fp6, fake_quantize_fp6, make_w46_weight,
+                    quantize_fp6, quantize_int4, select_outlier_columns)
+
+__all__ = [
+    "prepacking", "quantize", "dequantize", "mul",
+    "b200_sizes", "pack_b200", "unpack_b200", "repack_from_reference", "schedule", "dump_operands",
+    "device_status", "W46Weight", "make_w46_weight", "quantize_int4", "quantize_fp6", "encode_fp6",
+    "decode_fp6", "fake_quantize_fp6", "select_outlier_columns",
+]

@@ -1,0 +1,76 @@
+"""Builds fp6_marlin_b200/libfp6m.so in-tree with nvcc for sm_100a (no GPU needed to compile).
+
+Usage:  python fp6_marlin_b200/build.py [--force] [--verbose]   (run as a script: it must work
+before the package itself can be imported)
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG_DIR, "csrc")
+LIB_PATH = os.path.join(PKG_DIR, "libfp6m.so")
+OBJ_DIR = os.path.join(PKG_DIR, "build")
+
+CUDA_SOURCES = ["c_api.cu", "gemm_mma.cu", "dump_operands.cu"]
+HOST_SOURCES = ["host_pack.cpp"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cand = os.path.join(cuda_home, "bin", "nvcc")
+    return cand if os.path.isfile(cand) else (shutil.which("nvcc") or "nvcc")
+
+
+def _sources() -> list[str]:
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    headers.append(os.path.join(os.path.dirname(PKG_DIR), "include", "fp6m.h"))
+    return [os.path.join(CSRC, f) for f in CUDA_SOURCES + HOST_SOURCES] + headers
+
+
+def needs_build() -> bool:
+    if not os.path.isfile(LIB_PATH):
+        return True
+    lib_time = os.path.getmtime(LIB_PATH)
+    return any(os.path.getmtime(s) > lib_time for s in _sources())
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every source to an object and link the shared library; returns its path."""
+    if not force and not needs_build():
+        return LIB_PATH
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    nvcc = _nvcc()
+    objs, procs = [], []
+    log = []
+    for src in CUDA_SOURCES + HOST_SOURCES:
+        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        objs.append(obj)
+        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    failed = False
+    for src, proc in procs:
+        out, _ = proc.communicate()
+        log.append(f"==== {src}\n{out}")
+        failed |= proc.returncode != 0
+    text = "\n".join(log)
+    with open(os.path.join(OBJ_DIR, "ptxas.log"), "w") as f:
+        f.write(text)
+    if failed or verbose:
+        print(text)
+    if failed:
+        raise RuntimeError("nvcc failed; see output above")
+    subprocess.run([nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart"], check=True)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,131 @@
+// GPU half of the C ABI (include/fp6m.h): argument validation that mirrors the reference's host
+// dispatcher, the stripe schedule, and the kernel launches.  No allocation, no synchronisation.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/fp6m.h"
+#include "fp6m_layout.h"
+#include "gemm_params.h"
+
+namespace {
+
+using namespace fp6m;
+
+thread_local char g_cuda_error[256] = "";
+
+int cuda_fail(cudaError_t e, const char* where) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", where, cudaGetErrorString(e));
+  return FP6M_ERR_CUDA;
+}
+
+int sm_count(int dev) {
+  static int cached[64] = {};
+  if (dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
+};
+
+}  // namespace
+
+extern "C" {
+
+size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
+  (void)M; (void)N; (void)K; (void)quant_cols;
+  int ctas = (sms > 0 && sms < kMaxCtas) ? sms : kMaxCtas;
+  size_t b = mma_scratch_bytes(ctas, mma_rows_per_pass());
+  return (b + 255) & ~(size_t)255;
+}
+
+int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+             void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
+             int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+             int quant_cols, int group_size, int layout, int* status_dev) {
+  // --- the checks of the reference dispatcher, in its order (fp6_marlin_cuda_kernel.cu:885-907)
+  if (M < 0 || N < 0 || K < 0) return FP6M_ERR_BAD_ARG;
+  if (thread_k == -1 || thread_n == -1) {
+    if (M <= 16) { thread_k = 128; thread_n = 128; } else { thread_k = 64; thread_n = 256; }
+  }
+  if (thread_k <= 0 || thread_n <= 0) return FP6M_ERR_KERN_SHAPE;
+  if (N % thread_n != 0 || K % thread_k != 0) return FP6M_ERR_PROB_SHAPE;
+  if (M == 0 || N == 0 || K == 0) return FP6M_OK;
+  // kernels exist for 128x128 tiles with at most 16 rows and for 64x256 tiles (:933-942)
+  const bool shape_ok = (thread_k == 128 && thread_n == 128 && M <= 16) || (thread_k == 64 && thread_n == 256);
+  if (!shape_ok) return FP6M_ERR_KERN_SHAPE;
+
+  // --- checks of this implementation
+  if (max_par < 1) max_par = 1;
+  if (workspace_bytes < (size_t)(N / 128) * max_par * 4) return FP6M_ERR_WORKSPACE;  // fp6_marlin_cuda.cpp:62-63
+  if (layout != FP6M_LAYOUT_B200) return FP6M_ERR_BAD_ARG;
+  if (!(group_size == 128 || group_size <= 0)) return FP6M_ERR_BAD_ARG;
+  const int qc = quant_cols < 0 ? 0 : quant_cols;
+  if (qc > N || qc % 8 || (N - qc) % 8 || K % 8) return FP6M_ERR_PROB_SHAPE;
+  if (group_size == 128 && K % 128) return FP6M_ERR_PROB_SHAPE;
+  if (!A || !B || !C || !s || !workspace || !scratch) return FP6M_ERR_BAD_ARG;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || !aligned16(s) || !aligned16(scratch)) return FP6M_ERR_BAD_ARG;
+
+  DeviceGuard guard(dev);
+  if (sms <= 0) sms = sm_count(dev);
+  if (sms <= 0) return cuda_fail(cudaGetLastError(), "cudaDeviceGetAttribute");
+  int ctas = sms < kMaxCtas ? sms : kMaxCtas;
+
+  MulParams p;
+  p.geo = make_geometry(K, N, qc, group_size);
+  const int strips = p.geo.strips4 + p.geo.strips6;
+  if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
+  if (ctas > strips * p.geo.k128) ctas = strips * p.geo.k128;
+  if (scratch_bytes < mma_scratch_bytes(ctas, mma_rows_per_pass())) return FP6M_ERR_SCRATCH;
+  make_schedule(p.geo, ctas, &p.sched);
+  p.B = static_cast<const uint8_t*>(B);
+  p.S = static_cast<const half*>(s);
+  p.N = N; p.K = K;
+  p.counters = static_cast<int*>(workspace);
+  p.partials = static_cast<float*>(scratch);
+  p.status = status_dev;
+
+  const int rows = mma_rows_per_pass();
+  for (int m0 = 0; m0 < M; m0 += rows) {
+    p.A = static_cast<const half*>(A) + (size_t)m0 * K;
+    p.C = static_cast<half*>(C) + (size_t)m0 * N;
+    p.M = (M - m0) < rows ? (M - m0) : rows;
+    cudaError_t e = launch_gemm_mma(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "w46_gemm_mma launch");
+  }
+  return FP6M_OK;
+}
+
+int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, int quant_cols,
+                       int group_size, int dev, void* stream) {
+  if (!B || !s || !W_out || N <= 0 || K <= 0) return FP6M_ERR_BAD_ARG;
+  if (!(group_size == 128 || group_size <= 0)) return FP6M_ERR_BAD_ARG;
+  const int qc = quant_cols < 0 ? 0 : quant_cols;
+  if (qc > N) return FP6M_ERR_BAD_ARG;
+  DeviceGuard guard(dev);
+  cudaError_t e = launch_dump_operands(static_cast<const uint8_t*>(B), static_cast<const half*>(s),
+                                       static_cast<half*>(W_out), make_geometry(K, N, qc, group_size),
+                                       static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FP6M_OK : cuda_fail(e, "dump_operands launch");
+}
+
+const char* fp6m_last_cuda_error(void) { return g_cuda_error; }
+
+const char* fp6m_version(void) { return "fp6m-b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

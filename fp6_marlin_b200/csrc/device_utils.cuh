@@ -1,0 +1,151 @@
+// Device-side building blocks for sm_100a: mbarrier + bulk-TMA wrappers with BOUNDED waits,
+// the in-register dequantisers, and the warp-level tensor-core instruction.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace fp6m {
+
+constexpr int kStatusTimeout = 8;  // == FP6M_ERR_TIMEOUT
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier ---------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Wait with a time limit (about one second of SM clock).  When the limit runs out the thread
+// records FP6M_ERR_TIMEOUT in *status, marks itself `dead` and carries on as if the wait had
+// succeeded: every address the kernels form is independent of loaded data, so the kernel still
+// terminates (with garbage results and a status the host reads) instead of hanging the GPU.
+// A dead thread skips all later waits.
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, bool& dead) {
+  if (dead) return;
+  if (mbar_try_wait(bar, parity)) return;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return;
+    if (clock64() - t0 > (1ll << 31)) break;
+  }
+  dead = true;
+  if (status) atomicExch(status, kStatusTimeout);
+}
+
+// ---- bulk TMA (1-D, global -> shared, completion on an mbarrier; no multicast) -----------------
+__device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Same with an L2 evict-first policy for data that is streamed once (the weights).
+__device__ __forceinline__ void tma_load_1d_stream(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                                   uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t make_evict_first_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// ---- named barrier among a subset of warps ---------------------------------------------------
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ---- logic / permute helpers -------------------------------------------------------------------
+template <int lut>
+__device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(r) : "r"(a), "r"(b), "r"(c), "n"(lut));
+  return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ uint32_t h2_as_u32(half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<half2*>(&u); }
+
+// ---- dequantisers -------------------------------------------------------------------------------
+// One INT4 word of the b200 layout (8 rows of one column) -> four half2 = the row pairs
+// (i0,i1), (i2,i3), (i4,i5), (i6,i7), each value exactly fp16(q - 8) * scale with ONE fp16 rounding.
+// q - 8 is built exactly with the 1024-offset trick (0x6400 | nibble = 1024 + nibble), the same
+// values the reference's dequant_8int4 produces (fp6_marlin_cuda_kernel.cu:249-286).
+__device__ __forceinline__ void dequant_int4_word(uint32_t q, half2 scale, uint32_t (&out)[4]) {
+  constexpr uint32_t kLo = 0x000f000f, kHi = 0x00f000f0, kMagic = 0x64006400;
+  constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
+  const half2 sub = u32_as_h2(0x64086408);      // 1032
+  const half2 mul = u32_as_h2(0x2c002c00);      // 1/16
+  const half2 add = u32_as_h2(0xd480d480);      // -72
+  uint32_t lo = lop3<kAndOr>(q, kLo, kMagic);
+  uint32_t hi = lop3<kAndOr>(q, kHi, kMagic);
+  out[0] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lo), sub), scale));
+  out[1] = h2_as_u32(__hmul2(__hfma2(u32_as_h2(hi), mul, add), scale));
+  q >>= 8;
+  lo = lop3<kAndOr>(q, kLo, kMagic);
+  hi = lop3<kAndOr>(q, kHi, kMagic);
+  out[2] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lo), sub), scale));
+  out[3] = h2_as_u32(__hmul2(__hfma2(u32_as_h2(hi), mul, add), scale));
+}
+
+// One FP6 4-bit-plane word plus its 2-bit-plane word (b200 layout) -> four half2, each value the
+// exact E3M2 value times the column scale with ONE fp16 rounding - bit-identical to
+// hmul(hmul(bits, 4096), scale) of dequantMatrix_fp6_to_fp16 (weight_prepacking.cpp:205-212)
+// because `scale4096` = scale * 2^12 is exact.  `rot` = 4 * (jr & 1) selects the word's two sets.
+__device__ __forceinline__ void dequant_fp6_word(uint32_t four, uint32_t two, int rot, half2 scale4096,
+                                                 uint32_t (&out)[4]) {
+  constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
+  const uint32_t r0 = __funnelshift_l(two, two, rot) & 0x90909090u;
+  const uint32_t r1 = __funnelshift_l(two, two, rot + 2) & 0x90909090u;
+  const uint32_t x0 = lop3<kAndOr>(four, 0x0f0f0f0fu, r0);        // bytes `s00eeemm` of rows i0..i3
+  const uint32_t x1 = lop3<kAndOr>(four >> 4, 0x0f0f0f0fu, r1);   // rows i4..i7
+  out[0] = h2_as_u32(__hmul2(u32_as_h2(prmt(x0, 0u, 0x1404u)), scale4096));
+  out[1] = h2_as_u32(__hmul2(u32_as_h2(prmt(x0, 0u, 0x3424u)), scale4096));
+  out[2] = h2_as_u32(__hmul2(u32_as_h2(prmt(x1, 0u, 0x1404u)), scale4096));
+  out[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(x1, 0u, 0x3424u)), scale4096));
+}
+
+// ---- warp-level tensor-core tile: D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col) ------
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+}  // namespace fp6m

@@ -1,0 +1,166 @@
+// Blackwell weight layout ("b200", layout id 1) and the stripe schedule, shared by the host
+// packers, the kernels and the host dispatcher.
+//
+// Logical content is the reference's: a K x N weight matrix whose first N4 = N - qc columns are
+// INT4 codes q in 0..15 (value q - 8; fp6_marlin_cuda_kernel.cu:249-286) and whose last N6 = qc
+// columns are FP6 E3M2 codes `s eee mm` (weight_quant.cpp:27-96).  Only the tiling differs from
+// the reference's 16 x 64 chunk order (test.py:60-83, weight_prepacking.cpp:123-177).
+//
+// Tiling.  Each region (INT4, then FP6) is cut into STRIPS of 128 columns; the last strip of a
+// region may be narrower and is padded to a multiple of 32 columns (a "quad" = 4 tensor-core
+// column tiles of 8).  A strip is stored K-contiguously as K128 = ceil(K/128) BLOCKS; block
+// (strip, kb) covers rows [128 kb, 128 kb + 128) and holds nq quads:
+//
+//   INT4 block: nq * 2048 bytes.  u32 index ((w * nq + jq) * 32 + lane) * 4 + jr
+//       w  = 0..3   32-row window of the block
+//       jq = 0..nq-1, jr = 0..3   column tile j = 4 jq + jr
+//       lane = 4 g + t            the lane of a warp that consumes the word
+//     The word holds column 8 j + g of the strip, rows 128 kb + 32 w + 8 t + i (i = 0..7); nibble p
+//     (from the least significant) holds i = {0,2,4,6,1,3,5,7}[p], so `word & 0x000f000f` is the
+//     row pair (i0, i1), `word & 0x00f000f0` the pair (i2, i3), and the same after `>> 8`.
+//
+//   FP6 block: nq * 3072 bytes = a 4-bit plane (nq * 2048 bytes, indexed exactly as above) followed
+//     by a 2-bit plane (nq * 1024 bytes, u32 index ((w * nq + jq) * 32 + lane) * 2 + jr / 2).
+//     4-bit word: byte b has (code(i = b) & 15) in its low nibble and (code(i = 4 + b) & 15) in its
+//     high nibble.  2-bit word: for set js = 2 (jr & 1) + (i / 4) and byte b = i % 4, the sign bit of
+//     the code sits at bit (8 b + 7 - 2 js) mod 32 and the top exponent bit at (8 b + 4 - 2 js) mod 32,
+//     so that rotl(word, 2 js) & 0x90909090 supplies bits 7 and 4 of four bytes `s 0 0 e e e m m`.
+//
+// Rows >= K and columns past a region's width are padding: INT4 nibble 8 (value 0), FP6 code 0.
+//
+// Scales (fp16).  INT4: per strip, per group (group size 128 = one block; or a single group in
+// per-channel mode), 32 nq values ordered [g][j] (j = 0..4 nq - 1) for column 8 j + g.  FP6:
+// per-column scales after all INT4 scales, same [g][j] order per strip.
+#pragma once
+
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define FP6M_HD __host__ __device__ inline
+#else
+#define FP6M_HD inline
+#endif
+
+namespace fp6m {
+
+constexpr int kStripCols = 128;      // columns per full strip
+constexpr int kBlockRows = 128;      // rows per block (= the INT4 scale group)
+constexpr int kQuadCols = 32;        // padding granularity of a strip
+constexpr int kInt4QuadBytes = 2048; // one quad of one block, INT4
+constexpr int kFp6QuadBytes = 3072;  // one quad of one block, FP6 (2048 four-bit + 1024 two-bit)
+constexpr int kMaxCtas = 320;        // upper bound on the persistent grid
+
+constexpr int kLayoutReference = 0;
+constexpr int kLayoutB200 = 1;
+
+FP6M_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Geometry of one problem in the b200 layout.
+struct Geometry {
+  int K, N, qc;            // qc = number of FP6 columns (0 = INT4 only)
+  int n4, n6;              // columns per region
+  int k128;                // blocks per strip
+  int strips4, strips6;    // strips per region
+  int groups;              // scale groups along K for INT4: k128 (group 128) or 1 (per-channel)
+};
+
+FP6M_HD Geometry make_geometry(int K, int N, int qc, int group_size) {
+  Geometry g;
+  g.K = K; g.N = N; g.qc = qc < 0 ? 0 : qc;
+  g.n6 = g.qc; g.n4 = N - g.qc;
+  g.k128 = ceil_div(K, kBlockRows);
+  g.strips4 = ceil_div(g.n4, kStripCols);
+  g.strips6 = ceil_div(g.n6, kStripCols);
+  g.groups = group_size > 0 ? g.k128 : 1;
+  return g;
+}
+
+// Number of quads (32-column units) of strip `s` of a region that is `n_cols` wide.
+FP6M_HD int strip_quads(int n_cols, int s) {
+  int left = n_cols - s * kStripCols;
+  if (left >= kStripCols) return 4;
+  return ceil_div(left, kQuadCols);
+}
+// Number of real (unpadded) columns of strip `s`.
+FP6M_HD int strip_cols(int n_cols, int s) {
+  int left = n_cols - s * kStripCols;
+  return left >= kStripCols ? kStripCols : left;
+}
+
+// Byte offsets.  All full strips come first in a region, so a strip's offset is linear in s.
+FP6M_HD int64_t int4_region_bytes(const Geometry& g) {
+  return (int64_t)ceil_div(g.n4, kQuadCols) * g.k128 * kInt4QuadBytes;
+}
+FP6M_HD int64_t fp6_region_bytes(const Geometry& g) {
+  return (int64_t)ceil_div(g.n6, kQuadCols) * g.k128 * kFp6QuadBytes;
+}
+FP6M_HD int64_t weight_bytes(const Geometry& g) { return int4_region_bytes(g) + fp6_region_bytes(g); }
+
+FP6M_HD int64_t int4_block_offset(const Geometry& g, int strip, int kb) {
+  return ((int64_t)strip * 4 * g.k128 + (int64_t)kb * strip_quads(g.n4, strip)) * kInt4QuadBytes;
+}
+FP6M_HD int64_t fp6_block_offset(const Geometry& g, int strip, int kb) {
+  return int4_region_bytes(g) +
+         ((int64_t)strip * 4 * g.k128 + (int64_t)kb * strip_quads(g.n6, strip)) * kFp6QuadBytes;
+}
+
+// Scale element (fp16) offsets.
+FP6M_HD int64_t int4_scale_count(const Geometry& g) {
+  return (int64_t)ceil_div(g.n4, kQuadCols) * kQuadCols * g.groups;
+}
+FP6M_HD int64_t fp6_scale_count(const Geometry& g) { return (int64_t)ceil_div(g.n6, kQuadCols) * kQuadCols; }
+FP6M_HD int64_t scale_count(const Geometry& g) { return int4_scale_count(g) + fp6_scale_count(g); }
+FP6M_HD int64_t int4_scale_offset(const Geometry& g, int strip, int group) {
+  return ((int64_t)strip * kStripCols * g.groups) + (int64_t)group * strip_quads(g.n4, strip) * kQuadCols;
+}
+FP6M_HD int64_t fp6_scale_offset(const Geometry& g, int strip) {
+  return int4_scale_count(g) + (int64_t)strip * kStripCols;
+}
+
+// Position of a nibble inside an INT4 word for row offset i (0..7).
+FP6M_HD int int4_nibble_pos(int i) { return (i & 1) ? 4 + (i >> 1) : (i >> 1); }
+
+// ---------------------------------------------------------------------------------------------
+// Stripe schedule.  Blocks are ordered strip-major (INT4 strips, then FP6 strips), row-block
+// fastest, and weighted by the bytes they stream (2 units per INT4 quad, 3 per FP6 quad).  CTA c
+// owns the blocks [bound[c], bound[c+1]); a strip that is shared by several CTAs is reduced in
+// fp32 by the last of them to finish.  Replaces the reference's static INT4/FP6 SM split and its
+// stripe arithmetic (fp6_marlin_cuda_kernel.cu:308-408).
+// ---------------------------------------------------------------------------------------------
+struct Schedule {
+  int ctas;
+  int total_blocks;
+  int bound[kMaxCtas + 1];
+};
+
+FP6M_HD int block_cost(const Geometry& g, int strip_linear) {
+  return strip_linear < g.strips4 ? 2 * strip_quads(g.n4, strip_linear)
+                                  : 3 * strip_quads(g.n6, strip_linear - g.strips4);
+}
+
+inline void make_schedule(const Geometry& g, int ctas, Schedule* out) {
+  if (ctas > kMaxCtas) ctas = kMaxCtas;
+  if (ctas < 1) ctas = 1;
+  const int strips = g.strips4 + g.strips6;
+  const int total_blocks = strips * g.k128;
+  int64_t total_cost = 0;
+  for (int s = 0; s < strips; ++s) total_cost += (int64_t)block_cost(g, s) * g.k128;
+  out->ctas = ctas;
+  out->total_blocks = total_blocks;
+  // Walk the strips once; boundary c sits at the block whose cost interval contains c*T/ctas.
+  int s = 0;
+  int64_t strip_start_cost = 0;
+  for (int c = 0; c <= ctas; ++c) {
+    if (c == ctas) { out->bound[c] = total_blocks; break; }
+    int64_t target = total_cost * c / ctas;
+    while (s < strips && strip_start_cost + (int64_t)block_cost(g, s) * g.k128 <= target) {
+      strip_start_cost += (int64_t)block_cost(g, s) * g.k128;
+      ++s;
+    }
+    if (s >= strips) { out->bound[c] = total_blocks; continue; }
+    int kb = (int)((target - strip_start_cost) / block_cost(g, s));
+    out->bound[c] = s * g.k128 + kb;
+  }
+}
+
+}  // namespace fp6m

@@ -1,0 +1,34 @@
+// Parameter block shared by the host dispatcher and the GEMM kernels.  It travels by value in
+// kernel parameter space (no host-to-device copy, safe under stream capture).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fp6m_layout.h"
+
+namespace fp6m {
+
+struct MulParams {
+  const half* A;        // M x K, row-major
+  const uint8_t* B;     // packed weights, b200 layout
+  half* C;              // M x N, row-major
+  const half* S;        // scales, b200 order
+  int M, N, K;
+  Geometry geo;
+  int* counters;        // one zero-initialised int per strip (the caller's workspace)
+  float* partials;      // fp32 split-K slots (scratch)
+  int* status;          // optional device status word
+  Schedule sched;
+};
+
+// gemm_mma.cu
+int mma_rows_per_pass();
+size_t mma_scratch_bytes(int ctas, int rows_per_pass);
+cudaError_t launch_gemm_mma(const MulParams& p, cudaStream_t stream);
+
+// dump_operands.cu
+cudaError_t launch_dump_operands(const uint8_t* B, const half* S, half* W, const Geometry& geo, cudaStream_t stream);
+
+}  // namespace fp6m

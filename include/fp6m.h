@@ -1,0 +1,126 @@
+/*
+ * fp6m - C ABI of the B200-native W(4&6)A16 GEMM path.
+ *
+ * Plain pointers and sizes only; no torch types.  Every entry point names the reference interface
+ * it stands in for (paths are relative to the reference project).  All functions return one of
+ * the FP6M_* codes below unless stated otherwise.  Host functions never touch the GPU; GPU
+ * functions never allocate, never synchronise and never touch host memory: they enqueue work on
+ * the stream they are given, so the caller owns every buffer and every lifetime.
+ */
+#ifndef FP6M_H_
+#define FP6M_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FP6M_OK = 0,
+  FP6M_ERR_PROB_SHAPE = 1,   /* same value and meaning as ERR_PROB_SHAPE, fp6_marlin_cuda_kernel.cu:861 */
+  FP6M_ERR_KERN_SHAPE = 2,   /* same value and meaning as ERR_KERN_SHAPE, fp6_marlin_cuda_kernel.cu:862 */
+  FP6M_ERR_VALUE_RANGE = 3,  /* a value cannot be represented in FP6 (weight_quant.cpp:48-53 throws) */
+  FP6M_ERR_BAD_ARG = 4,      /* null / misaligned pointer, bad size, unknown layout or group size */
+  FP6M_ERR_WORKSPACE = 5,    /* workspace smaller than the reference demands (fp6_marlin_cuda.cpp:62-63) */
+  FP6M_ERR_SCRATCH = 6,      /* scratch buffer smaller than fp6m_mul_scratch_bytes() */
+  FP6M_ERR_CUDA = 7,         /* a CUDA runtime call failed; see fp6m_last_cuda_error() */
+  FP6M_ERR_TIMEOUT = 8       /* device status word: a bounded wait inside a kernel ran out */
+};
+
+enum { FP6M_LAYOUT_REFERENCE = 0, FP6M_LAYOUT_B200 = 1 };
+
+/* ------------------------------------------------------------------------------------------ */
+/* Host side: weight preparation                                                              */
+/* ------------------------------------------------------------------------------------------ */
+
+/* fp16 -> dense FP6 E3M2 stream, rows*cols*6/8 bytes, truncating cast, byte-identical to
+ * weight_prepacking_fp16_to_fp6 (fp6_marlin/weight_quant.cpp:106-124; binding pybind.cpp:42-59).
+ * The row-major memory of `w` is packed as it lies.  cols must be a multiple of 4.
+ * FP6M_ERR_VALUE_RANGE replaces the reference's std::invalid_argument. */
+int fp6m_quantize_fp6(const uint16_t* w, uint8_t* out, size_t rows, size_t cols);
+
+/* fp16 -> one FP6 E3M2 code (0..63) per byte, `count` values; the per-element half of
+ * cast_fp16_fp6 (fp6_marlin/weight_quant.cpp:27-91) without the 4-in-3 byte packing. */
+int fp6m_encode_fp6(const uint16_t* w, uint8_t* codes, size_t count);
+
+/* FP6 stream viewed as (n rows, k cols) -> the reference's "2+4" tensor-core layout (k*n*3/4
+ * bytes), byte-identical to weight_matrix_prepacking (fp6_marlin/weight_prepacking.cpp:123-177;
+ * binding pybind.cpp:18-31).  n and k must be multiples of 64. */
+int fp6m_prepack_fp6(const uint8_t* fp6, uint8_t* out, size_t n, size_t k);
+
+/* FP6 stream (n rows, k cols) and a per-row fp16 scale -> (n, k) fp16, bit-identical to
+ * dequantMatrix_fp6_to_fp16 (fp6_marlin/weight_prepacking.cpp:180-217; binding pybind.cpp:70-87). */
+int fp6m_dequant_fp6(const uint8_t* fp6, const uint16_t* scale, uint16_t* out, size_t n, size_t k);
+
+/* Sizes of the b200 layout: bytes of the packed weight buffer and number of fp16 scales.
+ * group_size is 128 (INT4 group scales) or -1 (per-channel, the reference's only mode,
+ * fp6_marlin_cuda_kernel.cu:447-448).  qc = number of FP6 columns, -1 or 0 for none. */
+int64_t fp6m_b200_weight_bytes(int K, int N, int qc);
+int64_t fp6m_b200_scale_count(int K, int N, int qc, int group_size);
+
+/* Logical codes -> b200 layout.  q4: K x (N-qc) INT4 codes 0..15 (uint8, row-major);
+ * c6: K x qc FP6 codes 0..63; s4: groups x (N-qc) fp16 scales (groups = ceil(K/128) or 1);
+ * s6: qc fp16 scales.  The counterpart of the packing half of gen_int4_weight / gen_mixed_weight
+ * (test.py:106-114, 123-152) for the Blackwell tiling. */
+int fp6m_pack_b200(const uint8_t* q4, const uint8_t* c6, const uint16_t* s4, const uint16_t* s6,
+                   int K, int N, int qc, int group_size, uint8_t* B_out, uint16_t* s_out);
+int fp6m_unpack_b200(const uint8_t* B, const uint16_t* s, int K, int N, int qc, int group_size,
+                     uint8_t* q4, uint8_t* c6, uint16_t* s4, uint16_t* s6);
+
+/* Reference-packed tensors (B = INT4 words then FP6 "2+4" words, s = permuted per-channel scales,
+ * exactly what gen_mixed_weight returns, test.py:123-152) -> logical codes and plain scales. */
+int fp6m_unpack_reference(const uint8_t* B_ref, const uint16_t* s_ref, int K, int N, int qc,
+                          uint8_t* q4, uint8_t* c6, uint16_t* s4, uint16_t* s6);
+/* Reference-packed tensors -> b200 layout (per-channel scales). */
+int fp6m_repack_from_reference(const uint8_t* B_ref, const uint16_t* s_ref, int K, int N, int qc,
+                               uint8_t* B_out, uint16_t* s_out);
+
+/* The stripe schedule the GEMM uses for this shape on `ctas` CTAs: writes ctas+1 block
+ * boundaries into `bounds` (see fp6m_layout.h).  Returns the number of blocks, or -1.
+ * Stands in for the reference's in-kernel stripe arithmetic (fp6_marlin_cuda_kernel.cu:308-408). */
+int fp6m_schedule(int K, int N, int qc, int group_size, int ctas, int* bounds);
+
+/* ------------------------------------------------------------------------------------------ */
+/* GPU side: the GEMM                                                                         */
+/* ------------------------------------------------------------------------------------------ */
+
+/* Bytes of scratch (device memory, any contents) fp6m_mul needs for this shape; 256-byte aligned. */
+size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms);
+
+/* C[M,N] (fp16, row-major, overwritten) = A[M,K] (fp16, row-major) x dequant(B, s).
+ * Stands in for fp6_marlin_cuda(...) (fp6_marlin/fp6_marlin_cuda_kernel.cu:864-951) as called from
+ * fp6_marlin_mul (fp6_marlin/fp6_marlin_cuda.cpp:47-92): same pointer roles, same tuning
+ * arguments (thread_k, thread_n, sms, max_par are validated exactly as the reference validates
+ * them and otherwise treated as hints), same return codes 0/1/2, asynchronous on `stream`.
+ *   workspace       >= N/128*max_par 32-bit words, all zero on entry, left all zero on exit
+ *                   (the reference's lock array; here it holds the per-strip arrival counters)
+ *   scratch         >= fp6m_mul_scratch_bytes(...) bytes of device memory for fp32 split-K partials
+ *   quant_cols      number of FP6 columns (last columns of B); -1 = none
+ *   group_size      128 or -1 (per-channel)
+ *   layout          FP6M_LAYOUT_B200 (FP6M_LAYOUT_REFERENCE is converted by
+ *                   fp6m_repack_from_reference on the host, or fp6m_repack_reference_gpu)
+ *   status_dev      optional device int: set to FP6M_ERR_TIMEOUT if a bounded wait ran out
+ * Output columns keep the order of B: INT4 columns first, FP6 columns last. */
+int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+             void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
+             int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+             int quant_cols, int group_size, int layout, int* status_dev);
+
+/* Debug: the fp16 operand tile the kernels feed the tensor cores, W_deq[K, N] row-major, produced by
+ * the same device dequantisation routines.  Lets a test prove bit-exactness against the reference
+ * dequantisers (dequant_8int4 / dequant_8fp6, fp6_marlin_cuda_kernel.cu:195-286). */
+int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, int quant_cols,
+                       int group_size, int dev, void* stream);
+
+/* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* fp6m_last_cuda_error(void);
+
+/* Library version tag, e.g. "fp6m-b200 0.1 (sm_100a)". */
+const char* fp6m_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP6M_H_ */

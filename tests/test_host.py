@@ -1,0 +1,233 @@
+"""CPU tests of the product's host side: the reference-compatible quantize / prepacking /
+dequantize, the b200 layout packers, the reference->b200 converter, the stripe schedule, and the
+C ABI surface.  No GPU compute is called here."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import fp6_marlin_b200 as fm
+from fp6_marlin_b200 import _lib
+from oracle import formats as F
+
+
+def _h(bits):
+    return np.asarray(bits).view(np.float16)
+
+
+# ---------------------------------------------------------------- C ABI surface
+def test_library_exports_every_declared_symbol():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "fp6m.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(fp6m_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(raw, name), f"{name} is declared in include/fp6m.h but not exported"
+    assert declared == set(_lib.SIGNATURES), "python binding and header disagree"
+    assert "sm_100a" in _lib.lib.fp6m_version().decode()
+
+
+def test_drop_in_module_surface():
+    import inspect
+
+    import fp6_marlin
+    for name in ("prepacking", "quantize", "dequantize", "mul"):
+        assert callable(getattr(fp6_marlin, name))
+    sig = inspect.signature(fp6_marlin.mul)
+    names = list(sig.parameters)
+    assert names[:10] == ["A", "B", "C", "s", "workspace", "quant_cols", "thread_k", "thread_n", "sms", "max_par"]
+    defaults = [sig.parameters[n].default for n in names[5:10]]
+    assert defaults == [-1, -1, -1, -1, 16]          # fp6_marlin/__init__.py:39
+
+
+# ---------------------------------------------------------------- reference-compatible host functions
+def test_host_functions_match_reference_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "fp6_host_256x256.npz"))
+    w = torch.from_numpy(_h(g["w"]).copy())
+    s = torch.from_numpy(_h(g["s"]).copy())
+    q = fm.quantize(w)
+    assert q.dtype == torch.int32 and tuple(q.shape) == (256, 48)
+    assert np.array_equal(q.numpy(), g["quantized"])
+    p = fm.prepacking(q)
+    assert tuple(p.shape) == (24, 512) and np.array_equal(p.numpy(), g["prepacked"])
+    d = fm.dequantize(q, s)
+    assert tuple(d.shape) == (256, 256) and np.array_equal(d.numpy().view(np.uint16), g["dequantized"])
+
+
+def test_host_functions_match_oracle_rectangular():
+    rng = np.random.default_rng(5)
+    w = rng.uniform(-28, 28, size=(512, 256)).astype(np.float16)
+    w = np.where(np.abs(w) < np.float16(0.0625), np.float16(0), w).astype(np.float16)
+    q = fm.quantize(torch.from_numpy(w))
+    assert tuple(q.shape) == (256, 96)
+    assert np.array_equal(q.numpy(), F.fp6_quantize(w))
+    s = rng.uniform(0.01, 1.0, size=256).astype(np.float16)
+    assert np.array_equal(fm.dequantize(q, torch.from_numpy(s)).numpy().view(np.uint16),
+                          F.fp6_dequant(q.numpy(), s).view(np.uint16))
+    assert np.array_equal(fm.prepacking(q).numpy(), F.fp6_prepack_reference(q.numpy()))
+
+
+def test_quantize_errors():
+    with pytest.raises(ValueError, match="float16"):
+        fm.quantize(torch.zeros(256, 256, dtype=torch.float32))
+    with pytest.raises(ValueError, match="out of range"):
+        fm.quantize(torch.full((256, 256), 30.0, dtype=torch.float16))
+    with pytest.raises(ValueError, match="out of range"):
+        fm.quantize(torch.full((256, 256), 0.01, dtype=torch.float16))
+    with pytest.raises(ValueError):
+        fm.quantize(torch.zeros(100, 256, dtype=torch.float16))      # the reference aborts here
+    with pytest.raises(ValueError):
+        fm.prepacking(torch.zeros(64, 48, dtype=torch.int32))
+    # zeros are fine
+    assert int(fm.quantize(torch.zeros(256, 256, dtype=torch.float16)).abs().sum()) == 0
+
+
+def test_encode_every_code():
+    codes = torch.arange(64, dtype=torch.uint8)
+    vals = fm.decode_fp6(codes)
+    keep = (codes & 0x1F) != 0                                   # +-0 both encode to their own sign
+    assert torch.equal(fm.encode_fp6(vals)[keep], codes[keep])
+    assert np.array_equal(vals.numpy().view(np.uint16), F.fp6_code_to_fp16_bits(codes.numpy()))
+
+
+# ---------------------------------------------------------------- quantisers against the oracle
+@pytest.mark.parametrize("group_size", [-1, 128])
+def test_int4_quantiser_matches_oracle(group_size):
+    torch.manual_seed(2)
+    w = (torch.randn(256, 96) * 0.02).half()
+    w[:, 5] = 0                                                  # an all-zero column / group
+    q, s, deq = fm.quantize_int4(w, group_size)
+    if group_size > 0:
+        qo, so, do = F.int4_quantize_group(w.numpy(), group_size)
+        assert np.array_equal(q.numpy(), qo) and np.array_equal(s.numpy().view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(deq.numpy().view(np.uint16), do.view(np.uint16))
+    else:
+        w[:, 5] = 0.01                                           # per-channel rule divides by the scale
+        q, s, deq = fm.quantize_int4(w, group_size)
+        qo, so, do = F.int4_quantize_per_channel(w.numpy())
+        assert np.array_equal(q.numpy(), qo) and np.array_equal(s.numpy().view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(deq.numpy().view(np.uint16), do.view(np.uint16))
+    assert np.array_equal(F.int4_dequant(q.numpy(), s.numpy(), group_size).view(np.uint16), deq.numpy().view(np.uint16))
+
+
+def test_fp6_quantiser_matches_oracle():
+    torch.manual_seed(4)
+    w = (torch.randn(128, 64) * 0.3).half()
+    c, s, deq = fm.quantize_fp6(w)
+    co, so, do = F.fp6_codes_and_dequant(w.numpy())
+    assert np.array_equal(c.numpy(), co) and np.array_equal(s.numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(deq.numpy().view(np.uint16), do.view(np.uint16))
+
+
+# ---------------------------------------------------------------- b200 layout
+B200_CASES = [(256, 512, 256, 128), (128, 160, 32, 128), (64, 96, 16, -1), (192, 64, 64, -1),
+              (256, 128, -1, 128), (256, 288, 288, -1), (384, 1280, 32, 128), (64, 8, -1, -1), (200, 264, 8, -1)]
+
+
+@pytest.mark.parametrize("k,n,qc,gs", B200_CASES)
+def test_b200_pack_unpack_round_trip(k, n, qc, gs):
+    rng = np.random.default_rng(k + n)
+    nq = max(qc, 0)
+    groups = (k + 127) // 128 if gs > 0 else 1
+    q4 = torch.from_numpy(rng.integers(0, 16, size=(k, n - nq), dtype=np.uint8))
+    c6 = torch.from_numpy(rng.integers(0, 64, size=(k, nq), dtype=np.uint8))
+    s4 = torch.from_numpy(rng.standard_normal((groups, n - nq)).astype(np.float16))
+    s6 = torch.from_numpy(rng.standard_normal(nq).astype(np.float16))
+    B, s = fm.pack_b200(q4 if n - nq else None, c6 if nq else None, s4 if n - nq else None, s6 if nq else None, k, n, qc, gs)
+    words, nscales = fm.b200_sizes(k, n, qc, gs)
+    assert B.numel() == words and s.numel() == nscales
+    r4, r6, rs4, rs6 = fm.unpack_b200(B, s, k, n, qc, gs)
+    assert torch.equal(r4, q4) and torch.equal(r6, c6)
+    assert torch.equal(rs4, s4) and torch.equal(rs6, s6)
+
+
+def test_b200_sizes_equal_reference_sizes_for_aligned_shapes():
+    # same bits, different tiling: for shapes the reference supports the byte counts agree
+    for (k, n, qc) in [(4096, 4096, 256), (8192, 8192, 256), (1024, 512, -1), (512, 256, 256)]:
+        nq = max(qc, 0)
+        words, nscales = fm.b200_sizes(k, n, qc, -1)
+        assert words * 4 == k * (n - nq) // 2 + k * nq * 3 // 4
+        assert nscales == n
+
+
+def test_b200_word_layout_by_hand():
+    """One INT4 word and one FP6 word decoded by the rules in fp6m_layout.h."""
+    k, n = 128, 64
+    q4 = torch.zeros((k, 32), dtype=torch.uint8) + 8
+    c6 = torch.zeros((k, 32), dtype=torch.uint8)
+    # column 9 = tile j=1, g=1; rows 40..47 = window 1, t=1
+    q4[40:48, 9] = torch.arange(1, 9, dtype=torch.uint8)
+    c6[40:48, 9] = torch.tensor([0b100001, 0b010010, 0b110011, 0b000100, 0b101111, 0b011010, 0b111001, 0b001000], dtype=torch.uint8)
+    B, _ = fm.pack_b200(q4, c6, torch.ones(1, 32).half(), torch.ones(32).half(), k, n, 32, -1)
+    words = B.numpy().view(np.uint32)
+    nq, w, jq, lane, jr = 1, 1, 0, 4 * 1 + 1, 1
+    word = int(words[((w * nq + jq) * 32 + lane) * 4 + jr])
+    nib = [(word >> (4 * p)) & 15 for p in range(8)]
+    assert nib == [1, 3, 5, 7, 2, 4, 6, 8]                        # rows i = 0,2,4,6,1,3,5,7
+    base = 2048 // 4                                             # FP6 region follows the INT4 block
+    four = int(words[base + ((w * nq + jq) * 32 + lane) * 4 + jr])
+    two = int(words[base + 2048 // 4 + ((w * nq + jq) * 32 + lane) * 2 + jr // 2])
+    codes = c6[40:48, 9].tolist()
+    for i in range(8):
+        b, js = i % 4, 2 * (jr & 1) + i // 4
+        lo = (four >> (8 * b + 4 * (i // 4))) & 15
+        rot = ((two << (2 * js)) | (two >> (32 - 2 * js))) & 0xFFFFFFFF if js else two
+        hi = (rot >> (8 * b)) & 0x90
+        assert lo == codes[i] & 15
+        assert hi == ((codes[i] >> 5) << 7 | ((codes[i] >> 4) & 1) << 4)
+
+
+@pytest.mark.parametrize("name", ["int4", "fp6", "mixed"])
+def test_repack_from_reference_golden(golden_dir, name):
+    """Tensors produced by the reference's own generators -> b200 layout -> logical codes equal the
+    codes the oracle derives from the same weights."""
+    g = np.load(os.path.join(golden_dir, "reference_generators.npz"))
+    k, n, qc = (int(x) for x in g[f"{name}_shape"])
+    nq = max(qc, 0)
+    B, s = fm.repack_from_reference(torch.from_numpy(g[f"{name}_packed"].copy()),
+                                    torch.from_numpy(_h(g[f"{name}_s"]).copy()), k, n, qc)
+    q4, c6, s4, s6 = fm.unpack_b200(B, s, k, n, qc, -1)
+    w = _h(g[f"{name}_w"])
+    wref = _h(g[f"{name}_wref"])
+    if n - nq:
+        qo, so, do = F.int4_quantize_per_channel(w[:, : n - nq])
+        assert np.array_equal(q4.numpy(), qo) and np.array_equal(s4.numpy().reshape(-1).view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(F.int4_dequant(q4.numpy(), s4.numpy().reshape(-1)).view(np.uint16), wref[:, : n - nq].view(np.uint16))
+    if nq:
+        vals = _h(F.fp6_code_to_fp16_bits(c6.numpy())).astype(np.float32)
+        deq = (vals * s6.numpy().astype(np.float32).reshape(1, -1)).astype(np.float16)
+        assert np.array_equal(deq.view(np.uint16), wref[:, n - nq:].view(np.uint16))
+
+
+# ---------------------------------------------------------------- stripe schedule
+@pytest.mark.parametrize("k,n,qc,ctas", [(8192, 8192, 256, 148), (4096, 4096, 256, 148), (11008, 4096, 256, 148),
+                                         (4096, 22016, 256, 148), (64, 256, -1, 148), (512, 256, 256, 148),
+                                         (8192, 1280, 32, 148), (1024, 25600, 256, 132), (256, 512, 256, 1),
+                                         (16384, 16384, 512, 296)])
+def test_schedule_covers_every_block_once(k, n, qc, ctas):
+    bounds, total = fm.schedule(k, n, qc, 128 if k % 128 == 0 else -1, ctas)
+    nq = max(qc, 0)
+    strips = -(-(n - nq) // 128) + -(-nq // 128)
+    assert total == strips * -(-k // 128)
+    assert bounds[0] == 0 and bounds[-1] == total and len(bounds) == ctas + 1
+    assert all(b1 >= b0 for b0, b1 in zip(bounds, bounds[1:]))
+    # byte balance: no CTA streams more than one block above the mean
+    k128 = -(-k // 128)
+    def cost(blk):
+        strip = blk // k128
+        s4 = -(-(n - nq) // 128)
+        if strip < s4:
+            cols = min(128, (n - nq) - strip * 128)
+            return 2 * -(-cols // 32)
+        cols = min(128, nq - (strip - s4) * 128)
+        return 3 * -(-cols // 32)
+    costs = np.array([cost(b) for b in range(total)], dtype=np.int64)
+    csum = np.concatenate([[0], np.cumsum(costs)])
+    per_cta = np.array([csum[b1] - csum[b0] for b0, b1 in zip(bounds, bounds[1:])])
+    assert per_cta.sum() == costs.sum()
+    assert per_cta.max() <= costs.sum() / ctas + 12 + 1e-9
