@@ -108,15 +108,21 @@ class W46Weight:
                          self.group_size, None if self.w_deq is None else self.w_deq.to(device))
 
 
-def make_w46_weight(w: torch.Tensor, quant_cols: int = -1, group_size: int = 128, keep_dequantized: bool = True) -> W46Weight:
+def make_w46_weight(w: torch.Tensor, quant_cols: int = -1, group_size: int = 128, keep_dequantized: bool = True,
+                    quant_device=None) -> W46Weight:
     """Quantise and pack fp16 W[k, n] whose last ``quant_cols`` columns are to be FP6 and the rest
-    INT4 - the counterpart of ``gen_mixed_weight`` (test.py:123-152) for the b200 layout."""
+    INT4 - the counterpart of ``gen_mixed_weight`` (test.py:123-152) for the b200 layout.
+    ``quant_device`` lets the elementwise INT4 rule run on a GPU (same IEEE fp16 arithmetic); the
+    result is a CPU-resident weight either way."""
     k, n = w.shape
     qc = max(quant_cols, 0)
     w4, w6 = w[:, : n - qc], w[:, n - qc:]
     q4 = s4 = d4 = c6 = s6 = d6 = None
     if n - qc > 0:
-        q4, s4, d4 = quantize_int4(w4.contiguous(), group_size)
+        src = w4.contiguous() if quant_device is None else w4.to(quant_device).contiguous()
+        q4, s4, d4 = (t.cpu() for t in quantize_int4(src, group_size))
+        if not keep_dequantized:
+            d4 = None
     if qc > 0:
         c6, s6, d6 = quantize_fp6(w6.contiguous())
     B, s = pack_b200(q4, c6, s4, s6, k, n, quant_cols, group_size)

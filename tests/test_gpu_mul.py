@@ -1,0 +1,177 @@
+"""GPU parity tests of the GEMM, through the C ABI (libfp6m.so) behind the reference-shaped Python
+API.  The checker is the oracle: W_deq from oracle/formats.py and C = A.float() @ W_deq.float()
+accumulated in fp32 on the CPU.  Tolerance: relative Frobenius error <= 1e-3 (the bar the
+benchmark configuration states; the reference's own tests use mean|dC|/mean|C| < 1e-3, test.py:181).
+Shapes follow the reference's tests (test.py:183-237) plus the sharded and ragged cases of the
+multi-GPU configurations."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import fp6_marlin
+import fp6_marlin_b200 as fm
+from fp6_marlin_b200 import synth
+from oracle import formats as F
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def _dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA GPU"
+    return torch.device("cuda:0")
+
+
+def _oracle_weight(w: torch.Tensor, qc: int, gs: int):
+    """W_deq by the oracle's rules, from the fp16 weights."""
+    k, n = w.shape
+    nq = max(qc, 0)
+    parts = []
+    if n - nq:
+        fn = (lambda x: F.int4_quantize_group(x, 128)) if gs > 0 else F.int4_quantize_per_channel
+        parts.append(fn(w[:, : n - nq].numpy())[2])
+    if nq:
+        parts.append(F.fp6_codes_and_dequant(w[:, n - nq:].numpy())[2])
+    return np.concatenate(parts, axis=1)
+
+
+def _run(m, k, n, qc, gs, thread_k=-1, thread_n=-1, seed=0, sms=-1):
+    dev = _dev()
+    w = synth.make_weight_fp16(k, n, qc, seed)
+    ww = fm.make_w46_weight(w, qc, gs, keep_dequantized=False).to(dev)
+    a = synth.make_activations(m, k, seed)
+    c = torch.zeros((m, n), dtype=torch.float16, device=dev)
+    workspace = torch.zeros(max(n // 128 * 16, 16), device=dev)       # float32 zeros, as test.py:168
+    fm.mul(a.to(dev), ww.B, c, ww.s, workspace, qc, thread_k, thread_n, sms, 16, group_size=gs, layout="b200")
+    torch.cuda.synchronize()
+    assert fm.device_status(dev) == 0
+    assert int(workspace.view(torch.int32).abs().sum()) == 0, "workspace must be left zeroed"
+    c_ref = F.gemm_reference(a.numpy(), _oracle_weight(w, qc, gs))
+    return F.rel_frobenius(c.cpu().numpy().astype(np.float32), c_ref), c
+
+
+def test_operands_are_bit_exact():
+    """The fp16 values fed to the tensor cores equal the oracle's dequantised weights bit for bit."""
+    dev = _dev()
+    for (k, n, qc, gs) in [(256, 512, 256, 128), (128, 160, 32, 128), (192, 320, 64, -1), (256, 256, 256, -1), (512, 384, -1, 128)]:
+        w = synth.make_weight_fp16(k, n, qc, seed=k + n)
+        ww = fm.make_w46_weight(w, qc, gs).to(dev)
+        dumped = fm.dump_operands(ww.B, ww.s, k, n, qc, gs).cpu().numpy()
+        assert np.array_equal(dumped.view(np.uint16), _oracle_weight(w, qc, gs).view(np.uint16)), (k, n, qc, gs)
+
+
+def test_every_fp6_code_dequantises_exactly():
+    dev = _dev()
+    k, n = 128, 64
+    codes = (torch.arange(k * n, dtype=torch.int32) % 64).to(torch.uint8).reshape(k, n)
+    s6 = torch.ones(n, dtype=torch.float16)
+    B, s = fm.pack_b200(None, codes, None, s6, k, n, n, -1)
+    dumped = fm.dump_operands(B.to(dev), s.to(dev), k, n, n, -1).cpu().numpy()
+    assert np.array_equal(dumped.view(np.uint16), F.fp6_code_to_fp16_bits(codes.numpy()))
+
+
+def test_config0_cpu_reference_case():
+    err, _ = _run(16, 4096, 4096, 256, 128)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 12, 16, 24, 32, 48, 64, 118, 128, 152])
+def test_tiles_int4_only(m):
+    # test.py:183-190: N=512, K=1024, both tile hints (128x128 only up to 16 rows)
+    for tk, tn in [(64, 256), (128, 128)]:
+        if m > 16 and tk == 128:
+            continue
+        err, _ = _run(m, 1024, 512, -1, -1, tk, tn)
+        assert err <= TOL, (m, tk, tn, err)
+
+
+@pytest.mark.parametrize("k", [768, 832, 896, 64, 128, 192])
+def test_k_not_multiple_of_pipeline_depth_and_tiny_k(k):
+    # test.py:192-200
+    err, _ = _run(16, k, 512, -1, -1, 64, 256)
+    assert err <= TOL, (k, err)
+
+
+@pytest.mark.parametrize("m", [1, 12, 16, 64, 65, 77, 152])
+@pytest.mark.parametrize("n,k", [(256, 512), (512, 1024), (25600, 1024)])
+def test_mixed(m, n, k):
+    # test.py:229-237: 256 FP6 columns; N=256 is the all-FP6 case
+    for gs in (-1, 128):
+        err, _ = _run(m, k, n, 256, gs, 64, 256)
+        assert err <= TOL, (m, n, k, gs, err)
+
+
+@pytest.mark.parametrize("m,k,n,qc", [(1, 8192, 1280, 32), (16, 8192, 1280, 32), (16, 4096, 2048, 16),
+                                      (5, 1024, 2688, 64), (16, 11008, 4096, 256), (32, 4096, 12288, 256)])
+def test_sharded_and_llama_shapes(m, k, n, qc):
+    # ragged strips: 1280-32 = 9.75 strips of INT4 columns, 16/32/64 FP6 columns
+    tk, tn = (64, 256) if n % 256 == 0 else (128, 128)
+    err, _ = _run(m, k, n, qc, 128, tk, tn)
+    assert err <= TOL, (m, k, n, qc, err)
+
+
+def test_few_ctas_and_repeatability():
+    e1, c1 = _run(16, 1024, 1024, 256, 128, sms=3)
+    e2, c2 = _run(16, 1024, 1024, 256, 128, sms=148)
+    e3, c3 = _run(16, 1024, 1024, 256, 128, sms=148)
+    assert max(e1, e2, e3) <= TOL
+    assert torch.equal(c2, c3), "the split-K reduction must be deterministic"
+
+
+def test_reference_layout_tensors_from_the_reference_generator(golden_dir):
+    """mul() on tensors packed by the reference's own gen_mixed_weight (golden fixture) equals
+    A @ W_ref with the reference's dequantised weights."""
+    dev = _dev()
+    g = np.load(os.path.join(golden_dir, "reference_generators.npz"))
+    for name in ("int4", "fp6", "mixed"):
+        k, n, qc = (int(x) for x in g[f"{name}_shape"])
+        B = torch.from_numpy(g[f"{name}_packed"].copy()).to(dev)
+        s = torch.from_numpy(g[f"{name}_s"].view(np.float16).copy()).to(dev)
+        a = synth.make_activations(16, k, 7)
+        c = torch.zeros((16, n), dtype=torch.float16, device=dev)
+        workspace = torch.zeros(n // 128 * 16, device=dev)
+        fp6_marlin.mul(a.to(dev), B, c, s, workspace, qc, 64, 256)
+        torch.cuda.synchronize()
+        c_ref = F.gemm_reference(a.numpy(), g[f"{name}_wref"].view(np.float16))
+        assert F.rel_frobenius(c.cpu().numpy().astype(np.float32), c_ref) <= TOL, name
+
+
+def test_errors_like_the_reference():
+    # test.py:202-227
+    dev = _dev()
+    m, n, k = 16, 256, 64
+    a = torch.randn((m, k), dtype=torch.half, device=dev)
+    ww = fm.make_w46_weight(synth.make_weight_fp16(k, n, -1), -1, -1).to(dev)
+    c = torch.zeros((m, n), dtype=torch.half, device=dev)
+    workspace = torch.zeros(n // 128, device=dev)
+    for tk, tn in [(128, 128), (256, 256)]:
+        with pytest.raises(RuntimeError):
+            fm.mul(a, ww.B, c, ww.s, torch.zeros(n // 128 * 16, device=dev), -1, tk, tn, -1, layout="b200")
+    with pytest.raises(RuntimeError, match="workspace"):
+        fm.mul(a, ww.B, c, ww.s, workspace, -1, 64, 256, -1, layout="b200")
+    with pytest.raises(RuntimeError):
+        fm.mul(a.cpu(), ww.B, c, ww.s, workspace, layout="b200")     # no CPU path
+    # zero-sized problems are silent no-ops (fp6_marlin_cuda_kernel.cu:906-907)
+    fm.mul(a[:0], ww.B, c[:0], ww.s, torch.zeros(32, device=dev), -1, 64, 256, layout="b200")
+
+
+def test_full_size_against_fp32_matmul_of_dumped_operands():
+    """K = N = 8192 (the benchmark layer): the operands the kernel uses are dumped, checked equal to
+    the product-side dequantised weights, and the result is compared with an fp32 matmul of them."""
+    dev = _dev()
+    k = n = 8192
+    layer = synth.make_layer(k, n, 256, 128, seed=1)
+    ww = layer.to(dev)
+    dumped = fm.dump_operands(ww.B, ww.s, k, n, 256, 128)
+    assert torch.equal(dumped, ww.w_deq)
+    for m in (1, 16, 64):
+        a = synth.make_activations(m, k, m).to(dev)
+        c = torch.zeros((m, n), dtype=torch.float16, device=dev)
+        workspace = torch.zeros(n // 128 * 16, device=dev)
+        fm.mul(a, ww.B, c, ww.s, workspace, 256, group_size=128, layout="b200")
+        c_ref = a.float() @ dumped.float()
+        err = (torch.linalg.norm(c.float() - c_ref) / torch.linalg.norm(c_ref)).item()
+        assert err <= TOL, (m, err)
+    assert fm.device_status(dev) == 0
