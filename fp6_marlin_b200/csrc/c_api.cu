@@ -50,7 +50,7 @@ extern "C" {
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
   (void)M; (void)N; (void)K; (void)quant_cols;
   int ctas = (sms > 0 && sms < kMaxCtas) ? sms : kMaxCtas;
-  size_t b = mma_scratch_bytes(ctas, mma_rows_per_pass());
+  size_t b = mma_scratch_bytes(ctas);
   return (b + 255) & ~(size_t)255;
 }
 
@@ -90,8 +90,8 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.geo = make_geometry(K, N, qc, group_size);
   const int strips = p.geo.strips4 + p.geo.strips6;
   if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
-  if (ctas > strips * p.geo.k128) ctas = strips * p.geo.k128;
-  if (scratch_bytes < mma_scratch_bytes(ctas, mma_rows_per_pass())) return FP6M_ERR_SCRATCH;
+  if (ctas > strips * units_per_strip(p.geo)) ctas = strips * units_per_strip(p.geo);
+  if (scratch_bytes < mma_scratch_bytes(ctas)) return FP6M_ERR_SCRATCH;
   make_schedule(p.geo, ctas, &p.sched);
   p.B = static_cast<const uint8_t*>(B);
   p.S = static_cast<const half*>(s);

@@ -34,10 +34,10 @@ __global__ void dump_operands_kernel(const uint8_t* __restrict__ B, const half* 
     uint2 two = make_uint2(0, 0);
     if (is6) two = reinterpret_cast<const uint2*>(base + nq * kInt4QuadBytes)[(w * nq + jq) * 32 + lane];
     const int group = (!is6 && geo.groups > 1) ? kb : 0;
-    const half* sp = S + (is6 ? fp6_scale_offset(geo, strip) : int4_scale_offset(geo, strip, group)) + g * 4 * nq + 4 * jq;
+    const half* sp = S + (is6 ? fp6_scale_offset(geo, strip) : int4_scale_offset(geo, strip, group));
     const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
     for (int jr = 0; jr < 4; ++jr) {
-      half2 s2 = __half2half2(sp[jr]);
+      half2 s2 = __half2half2(sp[scale_index(8 * (4 * jq + jr) + g, nq)]);
       uint32_t b[4];
       if (is6) {
         s2 = __hmul2(s2, k4096);

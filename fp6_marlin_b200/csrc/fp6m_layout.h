@@ -29,8 +29,10 @@
 // Rows >= K and columns past a region's width are padding: INT4 nibble 8 (value 0), FP6 code 0.
 //
 // Scales (fp16).  INT4: per strip, per group (group size 128 = one block; or a single group in
-// per-channel mode), 32 nq values ordered [g][j] (j = 0..4 nq - 1) for column 8 j + g.  FP6:
-// per-column scales after all INT4 scales, same [g][j] order per strip.
+// per-channel mode), 32 nq values ordered [t][j][e] (t = 0..3, j = 0..4 nq - 1, e = 0..1) for
+// column 8 j + 2 t + e - the two columns a lane holds of each accumulator tile, so a lane reads
+// the scales of four tiles with one 16-byte load.  FP6: per-column scales after all INT4 scales,
+// same order per strip.
 #pragma once
 
 #include <stdint.h>
@@ -117,50 +119,75 @@ FP6M_HD int64_t fp6_scale_offset(const Geometry& g, int strip) {
   return int4_scale_count(g) + (int64_t)strip * kStripCols;
 }
 
+// Index of column `c` (0..32 nq - 1) of a strip inside its block of 32 nq scales.
+FP6M_HD int scale_index(int c, int nq) { return (((c & 7) >> 1) * 4 * nq + (c >> 3)) * 2 + (c & 1); }
+
 // Position of a nibble inside an INT4 word for row offset i (0..7).
 FP6M_HD int int4_nibble_pos(int i) { return (i & 1) ? 4 + (i >> 1) : (i >> 1); }
 
 // ---------------------------------------------------------------------------------------------
-// Stripe schedule.  Blocks are ordered strip-major (INT4 strips, then FP6 strips), row-block
-// fastest, and weighted by the bytes they stream (2 units per INT4 quad, 3 per FP6 quad).  CTA c
-// owns the blocks [bound[c], bound[c+1]); a strip that is shared by several CTAs is reduced in
-// fp32 by the last of them to finish.  Replaces the reference's static INT4/FP6 SM split and its
-// stripe arithmetic (fp6_marlin_cuda_kernel.cu:308-408).
+// Stripe schedule.  The scheduling UNIT is half a block (64 rows of one strip).  Units are ordered
+// strip-major (INT4 strips, then FP6 strips), rows fastest, and weighted by the bytes they stream
+// (2 per INT4 quad, 3 per FP6 quad).  CTA c owns the units [bound[c], bound[c+1]) and splits them
+// evenly by weight among its warps; a strip that is shared by several CTAs is reduced in fp32 by
+// the last of them to finish.  Replaces the reference's static INT4/FP6 SM split and its stripe
+// arithmetic (fp6_marlin_cuda_kernel.cu:308-408).
 // ---------------------------------------------------------------------------------------------
+constexpr int kUnitRows = 64;
+
 struct Schedule {
   int ctas;
-  int total_blocks;
+  int total_units;
   int bound[kMaxCtas + 1];
 };
 
-FP6M_HD int block_cost(const Geometry& g, int strip_linear) {
+FP6M_HD int units_per_strip(const Geometry& g) { return 2 * g.k128; }
+
+FP6M_HD int unit_cost(const Geometry& g, int strip_linear) {
   return strip_linear < g.strips4 ? 2 * strip_quads(g.n4, strip_linear)
                                   : 3 * strip_quads(g.n6, strip_linear - g.strips4);
+}
+
+// First unit u in [u0, u1] such that the weight of [u0, u) is >= target (u1 if never).
+FP6M_HD int unit_at_cost(const Geometry& g, int u0, int u1, long long target) {
+  const int ups = units_per_strip(g);
+  int u = u0;
+  long long acc = 0;
+  while (u < u1) {
+    const int strip = u / ups;
+    const int c = unit_cost(g, strip);
+    int strip_end = (strip + 1) * ups;
+    if (strip_end > u1) strip_end = u1;
+    const long long span = (long long)(strip_end - u) * c;
+    if (acc + span <= target) { acc += span; u = strip_end; continue; }
+    return u + (int)((target - acc + c - 1) / c);
+  }
+  return u1;
+}
+
+FP6M_HD long long range_cost(const Geometry& g, int u0, int u1) {
+  const int ups = units_per_strip(g);
+  long long acc = 0;
+  int u = u0;
+  while (u < u1) {
+    const int strip = u / ups;
+    int strip_end = (strip + 1) * ups;
+    if (strip_end > u1) strip_end = u1;
+    acc += (long long)(strip_end - u) * unit_cost(g, strip);
+    u = strip_end;
+  }
+  return acc;
 }
 
 inline void make_schedule(const Geometry& g, int ctas, Schedule* out) {
   if (ctas > kMaxCtas) ctas = kMaxCtas;
   if (ctas < 1) ctas = 1;
-  const int strips = g.strips4 + g.strips6;
-  const int total_blocks = strips * g.k128;
-  int64_t total_cost = 0;
-  for (int s = 0; s < strips; ++s) total_cost += (int64_t)block_cost(g, s) * g.k128;
+  const int total_units = (g.strips4 + g.strips6) * units_per_strip(g);
+  const long long total_cost = range_cost(g, 0, total_units);
   out->ctas = ctas;
-  out->total_blocks = total_blocks;
-  // Walk the strips once; boundary c sits at the block whose cost interval contains c*T/ctas.
-  int s = 0;
-  int64_t strip_start_cost = 0;
-  for (int c = 0; c <= ctas; ++c) {
-    if (c == ctas) { out->bound[c] = total_blocks; break; }
-    int64_t target = total_cost * c / ctas;
-    while (s < strips && strip_start_cost + (int64_t)block_cost(g, s) * g.k128 <= target) {
-      strip_start_cost += (int64_t)block_cost(g, s) * g.k128;
-      ++s;
-    }
-    if (s >= strips) { out->bound[c] = total_blocks; continue; }
-    int kb = (int)((target - strip_start_cost) / block_cost(g, s));
-    out->bound[c] = s * g.k128 + kb;
-  }
+  out->total_units = total_units;
+  for (int c = 0; c <= ctas; ++c)
+    out->bound[c] = c == ctas ? total_units : unit_at_cost(g, 0, total_units, total_cost * c / ctas);
 }
 
 }  // namespace fp6m

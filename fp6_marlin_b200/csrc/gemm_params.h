@@ -25,7 +25,7 @@ struct MulParams {
 
 // gemm_mma.cu
 int mma_rows_per_pass();
-size_t mma_scratch_bytes(int ctas, int rows_per_pass);
+size_t mma_scratch_bytes(int ctas);
 cudaError_t launch_gemm_mma(const MulParams& p, cudaStream_t stream);
 
 // dump_operands.cu

@@ -300,21 +300,19 @@ int fp6m_pack_b200(const uint8_t* q4, const uint8_t* c6, const uint16_t* s4, con
     const int nq = strip_quads(geo.n4, strip);
     for (int grp = 0; grp < geo.groups; ++grp) {
       uint16_t* dst = s_out + int4_scale_offset(geo, strip, grp);
-      for (int g = 0; g < 8; ++g)
-        for (int j = 0; j < 4 * nq; ++j) {
-          const int col = strip * kStripCols + 8 * j + g;
-          dst[g * 4 * nq + j] = col < geo.n4 ? s4[(size_t)grp * geo.n4 + col] : one;
-        }
+      for (int c = 0; c < kQuadCols * nq; ++c) {
+        const int col = strip * kStripCols + c;
+        dst[scale_index(c, nq)] = col < geo.n4 ? s4[(size_t)grp * geo.n4 + col] : one;
+      }
     }
   }
   for (int strip = 0; strip < geo.strips6; ++strip) {
     const int nq = strip_quads(geo.n6, strip);
     uint16_t* dst = s_out + fp6_scale_offset(geo, strip);
-    for (int g = 0; g < 8; ++g)
-      for (int j = 0; j < 4 * nq; ++j) {
-        const int col = strip * kStripCols + 8 * j + g;
-        dst[g * 4 * nq + j] = col < geo.n6 ? s6[col] : one;
-      }
+    for (int c = 0; c < kQuadCols * nq; ++c) {
+      const int col = strip * kStripCols + c;
+      dst[scale_index(c, nq)] = col < geo.n6 ? s6[col] : one;
+    }
   }
   return FP6M_OK;
 }
@@ -345,11 +343,10 @@ int fp6m_unpack_b200(const uint8_t* B, const uint16_t* s, int K, int N, int qc, 
     }
     for (int grp = 0; grp < geo.groups; ++grp) {
       const uint16_t* src = s + int4_scale_offset(geo, strip, grp);
-      for (int g = 0; g < 8; ++g)
-        for (int j = 0; j < 4 * nq; ++j) {
-          const int col = strip * kStripCols + 8 * j + g;
-          if (col < geo.n4) s4[(size_t)grp * geo.n4 + col] = src[g * 4 * nq + j];
-        }
+      for (int c = 0; c < kQuadCols * nq; ++c) {
+        const int col = strip * kStripCols + c;
+        if (col < geo.n4) s4[(size_t)grp * geo.n4 + col] = src[scale_index(c, nq)];
+      }
     }
   }
   for (int strip = 0; strip < geo.strips6; ++strip) {
@@ -378,11 +375,10 @@ int fp6m_unpack_b200(const uint8_t* B, const uint16_t* s, int K, int N, int qc, 
             }
     }
     const uint16_t* src = s + fp6_scale_offset(geo, strip);
-    for (int g = 0; g < 8; ++g)
-      for (int j = 0; j < 4 * nq; ++j) {
-        const int col = strip * kStripCols + 8 * j + g;
-        if (col < geo.n6) s6[col] = src[g * 4 * nq + j];
-      }
+    for (int c = 0; c < kQuadCols * nq; ++c) {
+      const int col = strip * kStripCols + c;
+      if (col < geo.n6) s6[col] = src[scale_index(c, nq)];
+    }
   }
   return FP6M_OK;
 }
@@ -444,7 +440,7 @@ int fp6m_schedule(int K, int N, int qc, int group_size, int ctas, int* bounds) {
   Schedule sch;
   make_schedule(make_geometry(K, N, qc, group_size), ctas, &sch);
   for (int c = 0; c <= sch.ctas; ++c) bounds[c] = sch.bound[c];
-  return sch.total_blocks;
+  return sch.total_units;
 }
 
 }  // extern "C"

@@ -77,8 +77,9 @@ int fp6m_unpack_reference(const uint8_t* B_ref, const uint16_t* s_ref, int K, in
 int fp6m_repack_from_reference(const uint8_t* B_ref, const uint16_t* s_ref, int K, int N, int qc,
                                uint8_t* B_out, uint16_t* s_out);
 
-/* The stripe schedule the GEMM uses for this shape on `ctas` CTAs: writes ctas+1 block
- * boundaries into `bounds` (see fp6m_layout.h).  Returns the number of blocks, or -1.
+/* The stripe schedule the GEMM uses for this shape on `ctas` CTAs: writes ctas+1 boundaries, in
+ * units of 64 rows of one 128-column strip, into `bounds` (see fp6m_layout.h).  Returns the
+ * number of units, or -1.
  * Stands in for the reference's in-kernel stripe arithmetic (fp6_marlin_cuda_kernel.cu:308-408). */
 int fp6m_schedule(int K, int N, int qc, int group_size, int ctas, int* bounds);
 

@@ -72,6 +72,28 @@ def test_every_fp6_code_dequantises_exactly():
     assert np.array_equal(dumped.view(np.uint16), F.fp6_code_to_fp16_bits(codes.numpy()))
 
 
+def test_one_hot_rows_reproduce_the_dequantised_weights():
+    """With one-hot activation rows the GEMM returns rows of W: the kernel's zero-point correction,
+    group scaling and FP6 exponent handling (subnormal codes included) must reproduce the oracle's
+    dequantised weights exactly, since each output is a single product rounded once to fp16."""
+    dev = _dev()
+    for (k, n, qc, gs) in [(256, 512, 256, 128), (256, 384, 128, -1), (128, 256, 256, -1)]:
+        w = synth.make_weight_fp16(k, n, qc, seed=3)
+        w[:5, -3:] *= 0.01                                    # forces FP6 subnormals and zeros
+        ww = fm.make_w46_weight(w, qc, gs, keep_dequantized=False).to(dev)
+        w_deq = _oracle_weight(w, qc, gs)
+        rows = [0, 1, 2, 3, 4, 7, 8, 15, 31, 32, 63, 64, 100, 127, k - 2, k - 1]
+        a = torch.zeros((16, k), dtype=torch.float16)
+        for i, kk in enumerate(rows):
+            a[i, kk] = 1.0
+        c = torch.zeros((16, n), dtype=torch.float16, device=dev)
+        workspace = torch.zeros(n // 128 * 16, device=dev)
+        fm.mul(a.to(dev), ww.B, c, ww.s, workspace, qc, group_size=gs, layout="b200")
+        torch.cuda.synchronize()
+        # exact equality of values (+0 and -0 compare equal)
+        assert np.array_equal(c.cpu().numpy().astype(np.float32), w_deq[rows].astype(np.float32)), (k, n, qc, gs)
+
+
 def test_config0_cpu_reference_case():
     err, _ = _run(16, 4096, 4096, 256, 128)
     assert err <= TOL, err

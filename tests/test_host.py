@@ -209,24 +209,26 @@ def test_repack_from_reference_golden(golden_dir, name):
                                          (4096, 22016, 256, 148), (64, 256, -1, 148), (512, 256, 256, 148),
                                          (8192, 1280, 32, 148), (1024, 25600, 256, 132), (256, 512, 256, 1),
                                          (16384, 16384, 512, 296)])
-def test_schedule_covers_every_block_once(k, n, qc, ctas):
+def test_schedule_covers_every_unit_once(k, n, qc, ctas):
+    """Units are 64 rows of one 128-column strip; every unit belongs to exactly one CTA and the
+    byte weight per CTA is balanced to within one unit."""
     bounds, total = fm.schedule(k, n, qc, 128 if k % 128 == 0 else -1, ctas)
     nq = max(qc, 0)
-    strips = -(-(n - nq) // 128) + -(-nq // 128)
-    assert total == strips * -(-k // 128)
+    s4 = -(-(n - nq) // 128)
+    strips = s4 + -(-nq // 128)
+    ups = 2 * -(-k // 128)
+    assert total == strips * ups
     assert bounds[0] == 0 and bounds[-1] == total and len(bounds) == ctas + 1
     assert all(b1 >= b0 for b0, b1 in zip(bounds, bounds[1:]))
-    # byte balance: no CTA streams more than one block above the mean
-    k128 = -(-k // 128)
-    def cost(blk):
-        strip = blk // k128
-        s4 = -(-(n - nq) // 128)
+
+    def cost(unit):
+        strip = unit // ups
         if strip < s4:
             cols = min(128, (n - nq) - strip * 128)
             return 2 * -(-cols // 32)
         cols = min(128, nq - (strip - s4) * 128)
         return 3 * -(-cols // 32)
-    costs = np.array([cost(b) for b in range(total)], dtype=np.int64)
+    costs = np.array([cost(u) for u in range(total)], dtype=np.int64)
     csum = np.concatenate([[0], np.cumsum(costs)])
     per_cta = np.array([csum[b1] - csum[b0] for b0, b1 in zip(bounds, bounds[1:])])
     assert per_cta.sum() == costs.sum()
