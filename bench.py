@@ -78,7 +78,7 @@ class ClockSampler:
         self.proc = None
         cmd = ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"]
         if gpu_uuid:
-            cmd += ["-i", gpu_uuid]
+            cmd += ["-i", gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid]
         try:
             self.proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)

@@ -48,9 +48,9 @@ struct DeviceGuard {
 extern "C" {
 
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
-  (void)M; (void)N; (void)K; (void)quant_cols;
-  int ctas = (sms > 0 && sms < kMaxCtas) ? sms : kMaxCtas;
-  size_t b = mma_scratch_bytes(ctas);
+  (void)M; (void)N; (void)K; (void)quant_cols; (void)sms;
+  // upper bound over every configuration: the largest grid with the largest partial tile
+  size_t b = tc5_scratch_bytes(kMaxCtas, tc5_rows_per_pass());
   return (b + 255) & ~(size_t)255;
 }
 
@@ -84,14 +84,17 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   DeviceGuard guard(dev);
   if (sms <= 0) sms = sm_count(dev);
   if (sms <= 0) return cuda_fail(cudaGetLastError(), "cudaDeviceGetAttribute");
-  int ctas = sms < kMaxCtas ? sms : kMaxCtas;
+  const int rows = tc5_rows_per_pass();
+  const int pass_rows = M < rows ? M : rows;
+  long long want = (long long)sms * tc5_ctas_per_sm(pass_rows);
+  int ctas = want < kMaxCtas ? (int)want : kMaxCtas;
 
   MulParams p;
   p.geo = make_geometry(K, N, qc, group_size);
   const int strips = p.geo.strips4 + p.geo.strips6;
   if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
   if (ctas > strips * units_per_strip(p.geo)) ctas = strips * units_per_strip(p.geo);
-  if (scratch_bytes < mma_scratch_bytes(ctas)) return FP6M_ERR_SCRATCH;
+  if (scratch_bytes < tc5_scratch_bytes(ctas, pass_rows)) return FP6M_ERR_SCRATCH;
   make_schedule(p.geo, ctas, &p.sched);
   p.B = static_cast<const uint8_t*>(B);
   p.S = static_cast<const half*>(s);
@@ -100,13 +103,12 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.partials = static_cast<float*>(scratch);
   p.status = status_dev;
 
-  const int rows = mma_rows_per_pass();
   for (int m0 = 0; m0 < M; m0 += rows) {
     p.A = static_cast<const half*>(A) + (size_t)m0 * K;
     p.C = static_cast<half*>(C) + (size_t)m0 * N;
     p.M = (M - m0) < rows ? (M - m0) : rows;
-    cudaError_t e = launch_gemm_mma(p, static_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return cuda_fail(e, "w46_gemm_mma launch");
+    cudaError_t e = launch_gemm_tc5(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "w46_gemm_tc5 launch");
   }
   return FP6M_OK;
 }

@@ -4,35 +4,35 @@
 // Logical content is the reference's: a K x N weight matrix whose first N4 = N - qc columns are
 // INT4 codes q in 0..15 (value q - 8; fp6_marlin_cuda_kernel.cu:249-286) and whose last N6 = qc
 // columns are FP6 E3M2 codes `s eee mm` (weight_quant.cpp:27-96).  Only the tiling differs from
-// the reference's 16 x 64 chunk order (test.py:60-83, weight_prepacking.cpp:123-177).
+// the reference's 16 x 64 fragment order (test.py:60-83, weight_prepacking.cpp:123-177): on B200
+// the weights are the TMEM operand of tcgen05.mma, one TMEM lane = one weight column, so a thread
+// dequantises ONE column and the layout is column-major inside small units.
 //
 // Tiling.  Each region (INT4, then FP6) is cut into STRIPS of 128 columns; the last strip of a
-// region may be narrower and is padded to a multiple of 32 columns (a "quad" = 4 tensor-core
-// column tiles of 8).  A strip is stored K-contiguously as K128 = ceil(K/128) BLOCKS; block
-// (strip, kb) covers rows [128 kb, 128 kb + 128) and holds nq quads:
+// region may be narrower and is padded to a multiple of 32 columns (nq "quads" of 32).  Along K a
+// strip is a sequence of UNITS of 64 rows, stored one after the other (so any K range of a strip
+// is one contiguous range of HBM); two units form a BLOCK of 128 rows = one INT4 scale group.
 //
-//   INT4 block: nq * 2048 bytes.  u32 index ((w * nq + jq) * 32 + lane) * 4 + jr
-//       w  = 0..3   32-row window of the block
-//       jq = 0..nq-1, jr = 0..3   column tile j = 4 jq + jr
-//       lane = 4 g + t            the lane of a warp that consumes the word
-//     The word holds column 8 j + g of the strip, rows 128 kb + 32 w + 8 t + i (i = 0..7); nibble p
-//     (from the least significant) holds i = {0,2,4,6,1,3,5,7}[p], so `word & 0x000f000f` is the
-//     row pair (i0, i1), `word & 0x00f000f0` the pair (i2, i3), and the same after `>> 8`.
+//   INT4 unit: nq * 1024 bytes.  Column c (0 .. 32 nq - 1) owns 32 bytes at c * 32 = eight words;
+//     word w8 (0..7) holds rows 64 u + 8 w8 + i (i = 0..7) of that column, nibble p (from the least
+//     significant) holding i = {0,2,4,6,1,3,5,7}[p] - so `word & 0x000f000f` is the row pair
+//     (i0, i1), `word & 0x00f000f0` the pair (i2, i3), and the same after `>> 8`.
+//     Inside its 32 bytes word w8 sits at 16 * ((w8 >> 2) ^ ((c >> 2) & 1)) + 4 * (w8 & 3): the two
+//     16-byte halves are swapped for every other group of four columns, which makes a warp's
+//     16-byte loads (32 consecutive columns) free of shared-memory bank conflicts.
 //
-//   FP6 block: nq * 3072 bytes = a 4-bit plane (nq * 2048 bytes, indexed exactly as above) followed
-//     by a 2-bit plane (nq * 1024 bytes, u32 index ((w * nq + jq) * 32 + lane) * 2 + jr / 2).
-//     4-bit word: byte b has (code(i = b) & 15) in its low nibble and (code(i = 4 + b) & 15) in its
-//     high nibble.  2-bit word: for set js = 2 (jr & 1) + (i / 4) and byte b = i % 4, the sign bit of
-//     the code sits at bit (8 b + 7 - 2 js) mod 32 and the top exponent bit at (8 b + 4 - 2 js) mod 32,
-//     so that rotl(word, 2 js) & 0x90909090 supplies bits 7 and 4 of four bytes `s 0 0 e e e m m`.
+//   FP6 unit: nq * 1536 bytes = a four-bit part (nq * 1024 bytes, laid out exactly as above; byte b
+//     of word w8 has (code(i = b) & 15) in its low nibble and (code(i = 4 + b) & 15) in its high
+//     nibble) followed by a two-bit part (nq * 512 bytes; column c owns 16 bytes at c * 16 = four
+//     words; word w4 serves the four-bit words 2 w4 and 2 w4 + 1).  Two-bit word: for set
+//     js = 2 (w8 & 1) + (i / 4) and byte b = i % 4, the sign bit of the code sits at bit
+//     (8 b + 7 - 2 js) mod 32 and the top exponent bit at (8 b + 4 - 2 js) mod 32, so that
+//     rotl(word, 2 js) & 0x90909090 supplies bits 7 and 4 of four bytes `s 0 0 e e e m m`.
 //
 // Rows >= K and columns past a region's width are padding: INT4 nibble 8 (value 0), FP6 code 0.
 //
-// Scales (fp16).  INT4: per strip, per group (group size 128 = one block; or a single group in
-// per-channel mode), 32 nq values ordered [t][j][e] (t = 0..3, j = 0..4 nq - 1, e = 0..1) for
-// column 8 j + 2 t + e - the two columns a lane holds of each accumulator tile, so a lane reads
-// the scales of four tiles with one 16-byte load.  FP6: per-column scales after all INT4 scales,
-// same order per strip.
+// Scales (fp16), plain column order.  INT4: per strip, per group (group size 128 = one block; or a
+// single group in per-channel mode), 32 nq values.  FP6: per-column scales after all INT4 scales.
 #pragma once
 
 #include <stdint.h>
@@ -45,12 +45,13 @@
 
 namespace fp6m {
 
-constexpr int kStripCols = 128;      // columns per full strip
-constexpr int kBlockRows = 128;      // rows per block (= the INT4 scale group)
-constexpr int kQuadCols = 32;        // padding granularity of a strip
-constexpr int kInt4QuadBytes = 2048; // one quad of one block, INT4
-constexpr int kFp6QuadBytes = 3072;  // one quad of one block, FP6 (2048 four-bit + 1024 two-bit)
-constexpr int kMaxCtas = 320;        // upper bound on the persistent grid
+constexpr int kStripCols = 128;       // columns per full strip
+constexpr int kBlockRows = 128;       // rows per block (= the INT4 scale group)
+constexpr int kUnitRows = 64;         // rows per unit
+constexpr int kQuadCols = 32;         // padding granularity of a strip
+constexpr int kInt4UnitQuadBytes = 1024;  // one quad of one unit, INT4
+constexpr int kFp6UnitQuadBytes = 1536;   // one quad of one unit, FP6 (1024 four-bit + 512 two-bit)
+constexpr int kMaxCtas = 640;         // upper bound on the persistent grid
 
 constexpr int kLayoutReference = 0;
 constexpr int kLayoutB200 = 1;
@@ -77,7 +78,9 @@ FP6M_HD Geometry make_geometry(int K, int N, int qc, int group_size) {
   return g;
 }
 
-// Number of quads (32-column units) of strip `s` of a region that is `n_cols` wide.
+FP6M_HD int units_per_strip(const Geometry& g) { return 2 * g.k128; }
+
+// Number of quads (32-column groups) of strip `s` of a region that is `n_cols` wide.
 FP6M_HD int strip_quads(int n_cols, int s) {
   int left = n_cols - s * kStripCols;
   if (left >= kStripCols) return 4;
@@ -91,20 +94,22 @@ FP6M_HD int strip_cols(int n_cols, int s) {
 
 // Byte offsets.  All full strips come first in a region, so a strip's offset is linear in s.
 FP6M_HD int64_t int4_region_bytes(const Geometry& g) {
-  return (int64_t)ceil_div(g.n4, kQuadCols) * g.k128 * kInt4QuadBytes;
+  return (int64_t)ceil_div(g.n4, kQuadCols) * units_per_strip(g) * kInt4UnitQuadBytes;
 }
 FP6M_HD int64_t fp6_region_bytes(const Geometry& g) {
-  return (int64_t)ceil_div(g.n6, kQuadCols) * g.k128 * kFp6QuadBytes;
+  return (int64_t)ceil_div(g.n6, kQuadCols) * units_per_strip(g) * kFp6UnitQuadBytes;
 }
 FP6M_HD int64_t weight_bytes(const Geometry& g) { return int4_region_bytes(g) + fp6_region_bytes(g); }
 
-FP6M_HD int64_t int4_block_offset(const Geometry& g, int strip, int kb) {
-  return ((int64_t)strip * 4 * g.k128 + (int64_t)kb * strip_quads(g.n4, strip)) * kInt4QuadBytes;
+FP6M_HD int64_t int4_unit_offset(const Geometry& g, int strip, int unit) {
+  return ((int64_t)strip * 4 * units_per_strip(g) + (int64_t)unit * strip_quads(g.n4, strip)) * kInt4UnitQuadBytes;
 }
-FP6M_HD int64_t fp6_block_offset(const Geometry& g, int strip, int kb) {
+FP6M_HD int64_t fp6_unit_offset(const Geometry& g, int strip, int unit) {
   return int4_region_bytes(g) +
-         ((int64_t)strip * 4 * g.k128 + (int64_t)kb * strip_quads(g.n6, strip)) * kFp6QuadBytes;
+         ((int64_t)strip * 4 * units_per_strip(g) + (int64_t)unit * strip_quads(g.n6, strip)) * kFp6UnitQuadBytes;
 }
+// Byte offset of word w8 of column c inside the four-bit part of a unit.
+FP6M_HD int word_offset(int c, int w8) { return c * 32 + (((w8 >> 2) ^ ((c >> 2) & 1)) << 4) + ((w8 & 3) << 2); }
 
 // Scale element (fp16) offsets.
 FP6M_HD int64_t int4_scale_count(const Geometry& g) {
@@ -119,29 +124,21 @@ FP6M_HD int64_t fp6_scale_offset(const Geometry& g, int strip) {
   return int4_scale_count(g) + (int64_t)strip * kStripCols;
 }
 
-// Index of column `c` (0..32 nq - 1) of a strip inside its block of 32 nq scales.
-FP6M_HD int scale_index(int c, int nq) { return (((c & 7) >> 1) * 4 * nq + (c >> 3)) * 2 + (c & 1); }
-
 // Position of a nibble inside an INT4 word for row offset i (0..7).
 FP6M_HD int int4_nibble_pos(int i) { return (i & 1) ? 4 + (i >> 1) : (i >> 1); }
 
 // ---------------------------------------------------------------------------------------------
-// Stripe schedule.  The scheduling UNIT is half a block (64 rows of one strip).  Units are ordered
-// strip-major (INT4 strips, then FP6 strips), rows fastest, and weighted by the bytes they stream
-// (2 per INT4 quad, 3 per FP6 quad).  CTA c owns the units [bound[c], bound[c+1]) and splits them
-// evenly by weight among its warps; a strip that is shared by several CTAs is reduced in fp32 by
-// the last of them to finish.  Replaces the reference's static INT4/FP6 SM split and its stripe
+// Stripe schedule.  Units are ordered strip-major (INT4 strips, then FP6 strips), rows fastest,
+// and weighted by the bytes they stream (2 per INT4 quad, 3 per FP6 quad).  CTA c owns the units
+// [bound[c], bound[c+1]); a strip that is shared by several CTAs is reduced in fp32 by the last
+// of them to finish.  Replaces the reference's static INT4/FP6 SM split and its stripe
 // arithmetic (fp6_marlin_cuda_kernel.cu:308-408).
 // ---------------------------------------------------------------------------------------------
-constexpr int kUnitRows = 64;
-
 struct Schedule {
   int ctas;
   int total_units;
   int bound[kMaxCtas + 1];
 };
-
-FP6M_HD int units_per_strip(const Geometry& g) { return 2 * g.k128; }
 
 FP6M_HD int unit_cost(const Geometry& g, int strip_linear) {
   return strip_linear < g.strips4 ? 2 * strip_quads(g.n4, strip_linear)

@@ -23,10 +23,11 @@ struct MulParams {
   Schedule sched;
 };
 
-// gemm_mma.cu
-int mma_rows_per_pass();
-size_t mma_scratch_bytes(int ctas);
-cudaError_t launch_gemm_mma(const MulParams& p, cudaStream_t stream);
+// gemm_tc5.cu
+int tc5_rows_per_pass();
+int tc5_ctas_per_sm(int rows);
+size_t tc5_scratch_bytes(int ctas, int rows);
+cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 
 // dump_operands.cu
 cudaError_t launch_dump_operands(const uint8_t* B, const half* S, half* W, const Geometry& geo, cudaStream_t stream);

@@ -238,63 +238,56 @@ int fp6m_pack_b200(const uint8_t* q4, const uint8_t* c6, const uint16_t* s4, con
   if (!(group_size == 128 || group_size <= 0)) return FP6M_ERR_BAD_ARG;
   const Geometry geo = make_geometry(K, N, qc, group_size);
   if ((geo.n4 > 0 && (!q4 || !s4)) || (geo.n6 > 0 && (!c6 || !s6))) return FP6M_ERR_BAD_ARG;
+  const int ups = units_per_strip(geo);
 
-  // INT4 blocks
-  parallel_for((size_t)geo.strips4 * geo.k128, [=](size_t lo, size_t hi) {
+  // INT4 units
+  parallel_for((size_t)geo.strips4 * ups, [=](size_t lo, size_t hi) {
     for (size_t idx = lo; idx < hi; ++idx) {
-      const int strip = (int)(idx / geo.k128), kb = (int)(idx % geo.k128);
+      const int strip = (int)(idx / ups), unit = (int)(idx % ups);
       const int nq = strip_quads(geo.n4, strip);
-      uint32_t* blk = reinterpret_cast<uint32_t*>(B_out + int4_block_offset(geo, strip, kb));
-      for (int w = 0; w < 4; ++w)
-        for (int jq = 0; jq < nq; ++jq)
-          for (int lane = 0; lane < 32; ++lane)
-            for (int jr = 0; jr < 4; ++jr) {
-              const int g = lane >> 2, t = lane & 3;
-              const int col = strip * kStripCols + 8 * (4 * jq + jr) + g;
-              uint32_t word = 0;
-              for (int i = 0; i < 8; ++i) {
-                const int row = kb * kBlockRows + 32 * w + 8 * t + i;
-                uint32_t q = 8;
-                if (row < K && col < geo.n4) q = q4[(size_t)row * geo.n4 + col] & 15u;
-                word |= q << (4 * int4_nibble_pos(i));
-              }
-              blk[((w * nq + jq) * 32 + lane) * 4 + jr] = word;
-            }
-    }
-  });
-  // FP6 blocks
-  parallel_for((size_t)geo.strips6 * geo.k128, [=](size_t lo, size_t hi) {
-    for (size_t idx = lo; idx < hi; ++idx) {
-      const int strip = (int)(idx / geo.k128), kb = (int)(idx % geo.k128);
-      const int nq = strip_quads(geo.n6, strip);
-      uint8_t* base = B_out + fp6_block_offset(geo, strip, kb);
-      uint32_t* p4 = reinterpret_cast<uint32_t*>(base);
-      uint32_t* p2 = reinterpret_cast<uint32_t*>(base + (size_t)nq * kInt4QuadBytes);
-      for (int w = 0; w < 4; ++w)
-        for (int jq = 0; jq < nq; ++jq)
-          for (int lane = 0; lane < 32; ++lane) {
-            const int g = lane >> 2, t = lane & 3;
-            uint32_t two[2] = {0, 0};
-            for (int jr = 0; jr < 4; ++jr) {
-              const int col = strip * kStripCols + 8 * (4 * jq + jr) + g;
-              uint32_t four = 0;
-              for (int i = 0; i < 8; ++i) {
-                const int row = kb * kBlockRows + 32 * w + 8 * t + i;
-                uint32_t code = 0;
-                if (row < K && col < geo.n6) code = c6[(size_t)row * geo.n6 + col] & 63u;
-                const int b = i & 3, js = 2 * (jr & 1) + (i >> 2);
-                four |= (code & 15u) << (8 * b + 4 * (i >> 2));
-                two[jr >> 1] |= ((code >> 5) & 1u) << ((8 * b + 7 - 2 * js + 32) & 31);
-                two[jr >> 1] |= ((code >> 4) & 1u) << ((8 * b + 4 - 2 * js + 32) & 31);
-              }
-              p4[((w * nq + jq) * 32 + lane) * 4 + jr] = four;
-            }
-            p2[((w * nq + jq) * 32 + lane) * 2 + 0] = two[0];
-            p2[((w * nq + jq) * 32 + lane) * 2 + 1] = two[1];
+      uint8_t* base = B_out + int4_unit_offset(geo, strip, unit);
+      for (int c = 0; c < kQuadCols * nq; ++c)
+        for (int w8 = 0; w8 < 8; ++w8) {
+          const int col = strip * kStripCols + c;
+          uint32_t word = 0;
+          for (int i = 0; i < 8; ++i) {
+            const int row = unit * kUnitRows + 8 * w8 + i;
+            uint32_t q = 8;
+            if (row < K && col < geo.n4) q = q4[(size_t)row * geo.n4 + col] & 15u;
+            word |= q << (4 * int4_nibble_pos(i));
           }
+          std::memcpy(base + word_offset(c, w8), &word, 4);
+        }
     }
   });
-  // scales
+  // FP6 units
+  parallel_for((size_t)geo.strips6 * ups, [=](size_t lo, size_t hi) {
+    for (size_t idx = lo; idx < hi; ++idx) {
+      const int strip = (int)(idx / ups), unit = (int)(idx % ups);
+      const int nq = strip_quads(geo.n6, strip);
+      uint8_t* base = B_out + fp6_unit_offset(geo, strip, unit);
+      uint8_t* base2 = base + (size_t)nq * kInt4UnitQuadBytes;
+      for (int c = 0; c < kQuadCols * nq; ++c) {
+        const int col = strip * kStripCols + c;
+        uint32_t two[4] = {0, 0, 0, 0};
+        for (int w8 = 0; w8 < 8; ++w8) {
+          uint32_t four = 0;
+          for (int i = 0; i < 8; ++i) {
+            const int row = unit * kUnitRows + 8 * w8 + i;
+            uint32_t code = 0;
+            if (row < K && col < geo.n6) code = c6[(size_t)row * geo.n6 + col] & 63u;
+            const int b = i & 3, js = 2 * (w8 & 1) + (i >> 2);
+            four |= (code & 15u) << (8 * b + 4 * (i >> 2));
+            two[w8 >> 1] |= ((code >> 5) & 1u) << ((8 * b + 7 - 2 * js + 32) & 31);
+            two[w8 >> 1] |= ((code >> 4) & 1u) << ((8 * b + 4 - 2 * js + 32) & 31);
+          }
+          std::memcpy(base + word_offset(c, w8), &four, 4);
+        }
+        std::memcpy(base2 + c * 16, two, 16);
+      }
+    }
+  });
+  // scales, plain column order, padding columns get 1.0
   const uint16_t one = 0x3C00;
   for (int strip = 0; strip < geo.strips4; ++strip) {
     const int nq = strip_quads(geo.n4, strip);
@@ -302,7 +295,7 @@ int fp6m_pack_b200(const uint8_t* q4, const uint8_t* c6, const uint16_t* s4, con
       uint16_t* dst = s_out + int4_scale_offset(geo, strip, grp);
       for (int c = 0; c < kQuadCols * nq; ++c) {
         const int col = strip * kStripCols + c;
-        dst[scale_index(c, nq)] = col < geo.n4 ? s4[(size_t)grp * geo.n4 + col] : one;
+        dst[c] = col < geo.n4 ? s4[(size_t)grp * geo.n4 + col] : one;
       }
     }
   }
@@ -311,7 +304,7 @@ int fp6m_pack_b200(const uint8_t* q4, const uint8_t* c6, const uint16_t* s4, con
     uint16_t* dst = s_out + fp6_scale_offset(geo, strip);
     for (int c = 0; c < kQuadCols * nq; ++c) {
       const int col = strip * kStripCols + c;
-      dst[scale_index(c, nq)] = col < geo.n6 ? s6[col] : one;
+      dst[c] = col < geo.n6 ? s6[col] : one;
     }
   }
   return FP6M_OK;
@@ -323,61 +316,59 @@ int fp6m_unpack_b200(const uint8_t* B, const uint16_t* s, int K, int N, int qc, 
   if (!(group_size == 128 || group_size <= 0)) return FP6M_ERR_BAD_ARG;
   const Geometry geo = make_geometry(K, N, qc, group_size);
   if ((geo.n4 > 0 && (!q4 || !s4)) || (geo.n6 > 0 && (!c6 || !s6))) return FP6M_ERR_BAD_ARG;
+  const int ups = units_per_strip(geo);
   for (int strip = 0; strip < geo.strips4; ++strip) {
     const int nq = strip_quads(geo.n4, strip);
-    for (int kb = 0; kb < geo.k128; ++kb) {
-      const uint32_t* blk = reinterpret_cast<const uint32_t*>(B + int4_block_offset(geo, strip, kb));
-      for (int w = 0; w < 4; ++w)
-        for (int jq = 0; jq < nq; ++jq)
-          for (int lane = 0; lane < 32; ++lane)
-            for (int jr = 0; jr < 4; ++jr) {
-              const int g = lane >> 2, t = lane & 3;
-              const int col = strip * kStripCols + 8 * (4 * jq + jr) + g;
-              const uint32_t word = blk[((w * nq + jq) * 32 + lane) * 4 + jr];
-              for (int i = 0; i < 8; ++i) {
-                const int row = kb * kBlockRows + 32 * w + 8 * t + i;
-                if (row < K && col < geo.n4)
-                  q4[(size_t)row * geo.n4 + col] = (word >> (4 * int4_nibble_pos(i))) & 15u;
-              }
-            }
+    for (int unit = 0; unit < ups; ++unit) {
+      const uint8_t* base = B + int4_unit_offset(geo, strip, unit);
+      for (int c = 0; c < kQuadCols * nq; ++c)
+        for (int w8 = 0; w8 < 8; ++w8) {
+          const int col = strip * kStripCols + c;
+          uint32_t word;
+          std::memcpy(&word, base + word_offset(c, w8), 4);
+          for (int i = 0; i < 8; ++i) {
+            const int row = unit * kUnitRows + 8 * w8 + i;
+            if (row < K && col < geo.n4)
+              q4[(size_t)row * geo.n4 + col] = (word >> (4 * int4_nibble_pos(i))) & 15u;
+          }
+        }
     }
     for (int grp = 0; grp < geo.groups; ++grp) {
       const uint16_t* src = s + int4_scale_offset(geo, strip, grp);
       for (int c = 0; c < kQuadCols * nq; ++c) {
         const int col = strip * kStripCols + c;
-        if (col < geo.n4) s4[(size_t)grp * geo.n4 + col] = src[scale_index(c, nq)];
+        if (col < geo.n4) s4[(size_t)grp * geo.n4 + col] = src[c];
       }
     }
   }
   for (int strip = 0; strip < geo.strips6; ++strip) {
     const int nq = strip_quads(geo.n6, strip);
-    for (int kb = 0; kb < geo.k128; ++kb) {
-      const uint8_t* base = B + fp6_block_offset(geo, strip, kb);
-      const uint32_t* p4 = reinterpret_cast<const uint32_t*>(base);
-      const uint32_t* p2 = reinterpret_cast<const uint32_t*>(base + (size_t)nq * kInt4QuadBytes);
-      for (int w = 0; w < 4; ++w)
-        for (int jq = 0; jq < nq; ++jq)
-          for (int lane = 0; lane < 32; ++lane)
-            for (int jr = 0; jr < 4; ++jr) {
-              const int g = lane >> 2, t = lane & 3;
-              const int col = strip * kStripCols + 8 * (4 * jq + jr) + g;
-              const uint32_t four = p4[((w * nq + jq) * 32 + lane) * 4 + jr];
-              const uint32_t two = p2[((w * nq + jq) * 32 + lane) * 2 + (jr >> 1)];
-              for (int i = 0; i < 8; ++i) {
-                const int row = kb * kBlockRows + 32 * w + 8 * t + i;
-                const int b = i & 3, js = 2 * (jr & 1) + (i >> 2);
-                const uint32_t lo = (four >> (8 * b + 4 * (i >> 2))) & 15u;
-                const uint32_t sg = (two >> ((8 * b + 7 - 2 * js + 32) & 31)) & 1u;
-                const uint32_t e2 = (two >> ((8 * b + 4 - 2 * js + 32) & 31)) & 1u;
-                if (row < K && col < geo.n6)
-                  c6[(size_t)row * geo.n6 + col] = (uint8_t)((sg << 5) | (e2 << 4) | lo);
-              }
-            }
+    for (int unit = 0; unit < ups; ++unit) {
+      const uint8_t* base = B + fp6_unit_offset(geo, strip, unit);
+      const uint8_t* base2 = base + (size_t)nq * kInt4UnitQuadBytes;
+      for (int c = 0; c < kQuadCols * nq; ++c) {
+        const int col = strip * kStripCols + c;
+        uint32_t two[4];
+        std::memcpy(two, base2 + c * 16, 16);
+        for (int w8 = 0; w8 < 8; ++w8) {
+          uint32_t four;
+          std::memcpy(&four, base + word_offset(c, w8), 4);
+          for (int i = 0; i < 8; ++i) {
+            const int row = unit * kUnitRows + 8 * w8 + i;
+            const int b = i & 3, js = 2 * (w8 & 1) + (i >> 2);
+            const uint32_t lo = (four >> (8 * b + 4 * (i >> 2))) & 15u;
+            const uint32_t sg = (two[w8 >> 1] >> ((8 * b + 7 - 2 * js + 32) & 31)) & 1u;
+            const uint32_t e2 = (two[w8 >> 1] >> ((8 * b + 4 - 2 * js + 32) & 31)) & 1u;
+            if (row < K && col < geo.n6)
+              c6[(size_t)row * geo.n6 + col] = (uint8_t)((sg << 5) | (e2 << 4) | lo);
+          }
+        }
+      }
     }
     const uint16_t* src = s + fp6_scale_offset(geo, strip);
     for (int c = 0; c < kQuadCols * nq; ++c) {
       const int col = strip * kStripCols + c;
-      if (col < geo.n6) s6[col] = src[scale_index(c, nq)];
+      if (col < geo.n6) s6[col] = src[c];
     }
   }
   return FP6M_OK;

@@ -160,26 +160,28 @@ def test_b200_word_layout_by_hand():
     k, n = 128, 64
     q4 = torch.zeros((k, 32), dtype=torch.uint8) + 8
     c6 = torch.zeros((k, 32), dtype=torch.uint8)
-    # column 9 = tile j=1, g=1; rows 40..47 = window 1, t=1
-    q4[40:48, 9] = torch.arange(1, 9, dtype=torch.uint8)
-    c6[40:48, 9] = torch.tensor([0b100001, 0b010010, 0b110011, 0b000100, 0b101111, 0b011010, 0b111001, 0b001000], dtype=torch.uint8)
-    B, _ = fm.pack_b200(q4, c6, torch.ones(1, 32).half(), torch.ones(32).half(), k, n, 32, -1)
-    words = B.numpy().view(np.uint32)
-    nq, w, jq, lane, jr = 1, 1, 0, 4 * 1 + 1, 1
-    word = int(words[((w * nq + jq) * 32 + lane) * 4 + jr])
-    nib = [(word >> (4 * p)) & 15 for p in range(8)]
-    assert nib == [1, 3, 5, 7, 2, 4, 6, 8]                        # rows i = 0,2,4,6,1,3,5,7
-    base = 2048 // 4                                             # FP6 region follows the INT4 block
-    four = int(words[base + ((w * nq + jq) * 32 + lane) * 4 + jr])
-    two = int(words[base + 2048 // 4 + ((w * nq + jq) * 32 + lane) * 2 + jr // 2])
-    codes = c6[40:48, 9].tolist()
+    # column 9, rows 104..111 = unit 1 (rows 64..127), word w8 = 5
+    q4[104:112, 9] = torch.arange(1, 9, dtype=torch.uint8)
+    c6[104:112, 9] = torch.tensor([0b100001, 0b010010, 0b110011, 0b000100, 0b101111, 0b011010, 0b111001, 0b001000], dtype=torch.uint8)
+    B, s = fm.pack_b200(q4, c6, torch.ones(1, 32).half(), (torch.arange(32) + 1).half(), k, n, 32, -1)
+    raw = B.numpy().view(np.uint8)
+    nq, unit, c, w8 = 1, 1, 9, 5
+    off = unit * nq * 1024 + c * 32 + 16 * ((w8 >> 2) ^ ((c >> 2) & 1)) + 4 * (w8 & 3)
+    word = int(raw[off:off + 4].view(np.uint32)[0])
+    assert [(word >> (4 * p)) & 15 for p in range(8)] == [1, 3, 5, 7, 2, 4, 6, 8]     # rows i = 0,2,4,6,1,3,5,7
+    fp6_base = 2 * nq * 1024 + unit * nq * 1536                # INT4 region (two units), then FP6 units
+    four = int(raw[fp6_base + c * 32 + 16 * ((w8 >> 2) ^ ((c >> 2) & 1)) + 4 * (w8 & 3):][:4].view(np.uint32)[0])
+    two = int(raw[fp6_base + nq * 1024 + c * 16 + 4 * (w8 >> 1):][:4].view(np.uint32)[0])
+    codes = c6[104:112, 9].tolist()
     for i in range(8):
-        b, js = i % 4, 2 * (jr & 1) + i // 4
+        b, js = i % 4, 2 * (w8 & 1) + i // 4
         lo = (four >> (8 * b + 4 * (i // 4))) & 15
         rot = ((two << (2 * js)) | (two >> (32 - 2 * js))) & 0xFFFFFFFF if js else two
         hi = (rot >> (8 * b)) & 0x90
         assert lo == codes[i] & 15
         assert hi == ((codes[i] >> 5) << 7 | ((codes[i] >> 4) & 1) << 4)
+    # scales are in plain column order: INT4 scales (padded to 32), then FP6 scales
+    assert s.numel() == 64 and float(s[32 + 9]) == 10.0
 
 
 @pytest.mark.parametrize("name", ["int4", "fp6", "mixed"])
