@@ -93,7 +93,14 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.geo = make_geometry(K, N, qc, group_size);
   const int strips = p.geo.strips4 + p.geo.strips6;
   if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
-  if (ctas > strips * units_per_strip(p.geo)) ctas = strips * units_per_strip(p.geo);
+  {
+    // keep at least ~12 units per CTA (but use every SM) so that few CTAs share a strip
+    const int total_units = strips * units_per_strip(p.geo);
+    int by_work = total_units / (12);
+    if (by_work < sms) by_work = sms;
+    if (ctas > by_work) ctas = by_work;
+    if (ctas > total_units) ctas = total_units;
+  }
   if (scratch_bytes < tc5_scratch_bytes(ctas, pass_rows)) return FP6M_ERR_SCRATCH;
   make_schedule(p.geo, ctas, &p.sched);
   p.B = static_cast<const uint8_t*>(B);

@@ -40,21 +40,50 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait with a time limit (about one second of SM clock).  When the limit runs out the thread
-// records FP6M_ERR_TIMEOUT in *status, marks itself `dead` and carries on as if the wait had
-// succeeded: every address the kernels form is independent of loaded data, so the kernel still
-// terminates (with garbage results and a status the host reads) instead of hanging the GPU.
-// A dead thread skips all later waits.
+// try_wait with a suspend-time hint: the hardware may park the thread until the phase completes or
+// the hint (nanoseconds) runs out, instead of burning issue slots in a polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// Wait with a limit (about one second).  When the limit runs out the thread records
+// FP6M_ERR_TIMEOUT in *status, marks itself `dead` and carries on as if the wait had succeeded:
+// every address the kernels form is independent of loaded data, so the kernel still terminates
+// (with garbage results and a status the host reads) instead of hanging the GPU.  A dead thread
+// skips all later waits.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, bool& dead) {
   if (dead) return;
-  if (mbar_try_wait(bar, parity)) return;
-  const long long t0 = clock64();
-  while (true) {
+  if (mbar_test_wait(bar, parity)) return;
+  // a short tight poll (lowest wake-up latency), then parked waits
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return;
-    if (clock64() - t0 > (1ll << 31)) break;
-  }
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_test_wait(bar, parity)) return;
+#pragma unroll 1
+  for (int i = 0; i < (1 << 16); ++i)
+    if (mbar_try_wait_hint(bar, parity, 16384u)) return;     // up to 65536 x 16 us
   dead = true;
   if (status) atomicExch(status, kStatusTimeout);
 }

@@ -14,12 +14,11 @@
 //               completion to mbarriers; the warp also owns the TMEM allocation.
 //   warps 2-5   dequantisers: thread = weight column = TMEM lane.  A thread reads its 32 bytes of
 //               a unit, expands the eight words in registers and stores them with tcgen05.st into
-//               a two-slot TMEM operand ring.  INT4 nibbles are OR-ed into fp16 constants
-//               (1024 + q, 64 + q: exact) and a second MMA per K step with a constant TMEM tile of
-//               the negated constants removes them again, so TMEM accumulates sum a * (q - 8) - what
-//               the reference's dequant_8int4 feeds its tensor cores (fp6_marlin_cuda_kernel.cu:
-//               249-286) - at 5 ALU instructions per 8 weights.  FP6 codes become `s 00eee mm` fp16
-//               patterns (value / 4096, as dequant_8fp6 builds them, :195-237).  After every scale
+//               a small TMEM operand ring.  INT4 nibbles become the exact integers q - 8 in fp16
+//               (OR into 1024 + q / 64 + q, then subtract 1032 / 72) - bit for bit what the
+//               reference's dequant_8int4 feeds its tensor cores (fp6_marlin_cuda_kernel.cu:249-286).
+//               FP6 codes become `s 00eee mm` fp16 patterns (exact value / 4096, as dequant_8fp6
+//               builds them before its multiply by 4096, :195-237).  After every scale
 //               group (128 rows) the same threads read the accumulator tile back (tcgen05.ld),
 //               multiply by their column's group scale in fp32 and add to registers; two accumulator
 //               tiles alternate so the read-back overlaps the next group's MMAs.
@@ -44,9 +43,7 @@ constexpr int kDequantThreads = 128;
 constexpr int kUnitW = 6144;            // packed words of one unit: up to 4096 four-bit + 2048 two-bit
 constexpr int kUnitS = 256;             // group scales of the unit's block: 128 fp16
 constexpr int kActOffset = kUnitW + kUnitS;
-constexpr int kTmemSlots = 2;           // operand ring: 2 units x 4 K-steps x 8 columns
-constexpr uint32_t kNegBiasLo = 0xe408e408u;  // -1032, -1032
-constexpr uint32_t kNegBiasHi = 0xd480d480u;  // -72, -72
+constexpr int kTmemSlots = 3;           // operand ring: 3 units x 4 K-steps x 8 columns
 
 template <int NT_, int STAGES_, int CTAS_PER_SM_>
 struct Tc5Cfg {
@@ -58,7 +55,7 @@ struct Tc5Cfg {
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kNumBars = 2 * kStages + 2 * kTmemSlots + 4;
   static constexpr int kSmemBytes = kRingBytes + kNumBars * 8 + 64;
-  static constexpr int kTmemD0 = 0, kTmemD1 = NT, kTmemBias = 2 * NT, kTmemA = 2 * NT + 8;
+  static constexpr int kTmemD0 = 0, kTmemD1 = NT, kTmemA = 2 * NT;
   static constexpr int kTmemUsed = kTmemA + kTmemSlots * 32;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : 256;
   static constexpr int kSlotFloats = NT * kStripCols;
@@ -114,14 +111,17 @@ __device__ __forceinline__ int atomic_add_acq_rel(int* addr, int v) {
   return old;
 }
 
-// INT4 word -> 1024 + q (rows i0,i1 and i4,i5) and 64 + q (rows i2,i3 and i6,i7): exact fp16 values.
+// INT4 word -> the exact integers q - 8 as fp16 pairs (rows i0,i1 | i2,i3 | i4,i5 | i6,i7): the nibble is
+// OR-ed into the mantissa of 1024 (bits 0-3) or of 64 (bits 4-7) and the constant is subtracted.
 __device__ __forceinline__ void expand_int4(uint32_t q, uint32_t* b) {
   constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
-  b[0] = lop3<kAndOr>(q, 0x000f000fu, 0x64006400u);
-  b[1] = lop3<kAndOr>(q, 0x00f000f0u, 0x54005400u);
+  const half2 lo_bias = u32_as_h2(0x64086408u);   // 1032
+  const half2 hi_bias = u32_as_h2(0x54805480u);   // 72
+  b[0] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x000f000fu, 0x64006400u)), lo_bias));
+  b[1] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x00f000f0u, 0x54005400u)), hi_bias));
   q >>= 8;
-  b[2] = lop3<kAndOr>(q, 0x000f000fu, 0x64006400u);
-  b[3] = lop3<kAndOr>(q, 0x00f000f0u, 0x54005400u);
+  b[2] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x000f000fu, 0x64006400u)), lo_bias));
+  b[3] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x00f000f0u, 0x54005400u)), hi_bias));
 }
 // FP6 four-bit word + two-bit word -> `s 00eee mm 00000000` fp16 patterns (value / 4096).
 __device__ __forceinline__ void expand_fp6(uint32_t four, uint32_t two, int rot, uint32_t* b) {
@@ -206,53 +206,61 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
     it.init(U0, U1, ups);
     int stage = 0, phase = 0;
     int cur_strip = -1, nq = 0;
-    bool is6 = false, group = false;
-    const uint8_t* wsrc = nullptr;
-    const half* ssrc = nullptr;
-    int unit_bytes = 0;
+    bool group = false;
+    const uint8_t* wsrc = nullptr;      // next unit's packed words
+    const half* ssrc = nullptr;         // group scales of the strip's first block
+    uint32_t unit_bytes = 0, sbytes = 0;
+    // activations: this lane copies chunks idx = lane + 32 j: row m = idx / 8, 16-byte chunk kc = idx % 8
+    // of the unit, into canonical core-matrix order; everything but the K offset is loop-invariant
+    const half* a_src[NT / 4];
+    uint32_t a_dst[NT / 4];
+    bool a_row_ok[NT / 4];
+    const int kc = lane & 7;
+#pragma unroll
+    for (int j = 0; j < NT / 4; ++j) {
+      const int m = (lane >> 3) + 4 * j;
+      a_row_ok[j] = m < p.M;
+      a_src[j] = p.A + (size_t)(a_row_ok[j] ? m : 0) * p.K + 8 * kc;
+      a_dst[j] = kActOffset + (kc >> 1) * (NT / 8) * 256 + ((m >> 3) * 2 + (kc & 1)) * 128 + (m & 7) * 16;
+    }
+    uint32_t dst = smem_u32(smem), bar = full_w;
     for (; it.valid(); it.next()) {
       if (it.strip_lin != cur_strip) {
         cur_strip = it.strip_lin;
-        is6 = cur_strip >= geo.strips4;
+        const bool is6 = cur_strip >= geo.strips4;
         if (!is6) {
           nq = strip_quads(geo.n4, cur_strip);
-          wsrc = p.B + int4_unit_offset(geo, cur_strip, 0);
           unit_bytes = nq * kInt4UnitQuadBytes;
+          wsrc = p.B + int4_unit_offset(geo, cur_strip, 0) + (size_t)it.unit * unit_bytes;
           group = geo.groups > 1;
           ssrc = p.S + int4_scale_offset(geo, cur_strip, 0);
         } else {
           nq = strip_quads(geo.n6, cur_strip - geo.strips4);
-          wsrc = p.B + fp6_unit_offset(geo, cur_strip - geo.strips4, 0);
           unit_bytes = nq * kFp6UnitQuadBytes;
+          wsrc = p.B + fp6_unit_offset(geo, cur_strip - geo.strips4, 0) + (size_t)it.unit * unit_bytes;
           group = false;
         }
+        sbytes = group ? nq * 64 : 0;
       }
       mbar_wait_bounded(empty_w + 8 * stage, phase ^ 1, p.status, dead);
-      const uint32_t dst = smem_u32(smem + stage * C::kStageBytes);
-      const uint32_t bar = full_w + 8 * stage;
       if (lane == 0) {
-        const uint32_t sbytes = group ? nq * 64 : 0;
         mbar_arrive_expect_tx(bar, unit_bytes + sbytes);
-        tma_load_1d_stream(dst, wsrc + (size_t)it.unit * unit_bytes, unit_bytes, bar, policy);
-        if (group) tma_load_1d(dst + kUnitW, ssrc + (size_t)(it.unit >> 1) * nq * kQuadCols, sbytes, bar);
+        tma_load_1d_stream(dst, wsrc, unit_bytes, bar, policy);
+        if (group) tma_load_1d(dst + kUnitW, ssrc + (it.unit >> 1) * nq * kQuadCols, sbytes, bar);
       }
-      // activations of the unit: NT rows x 8 chunks of 16 bytes into canonical core-matrix order
+      wsrc += unit_bytes;
       const int k0 = it.unit * kUnitRows;
+      const bool k_ok = k0 + 8 * kc < p.K;
 #pragma unroll
       for (int j = 0; j < NT / 4; ++j) {
-        const int idx = lane + 32 * j;
-        const int m = idx >> 3, kc = idx & 7;
-        const int k = k0 + 8 * kc;
-        const bool ok = m < p.M && k < p.K;
-        const uint32_t off = kActOffset + (kc >> 1) * (NT / 8) * 256 + ((m >> 3) * 2 + (kc & 1)) * 128 + (m & 7) * 16;
-        cp_async16(dst + off, ok ? (const void*)(p.A + (size_t)m * p.K + k) : (const void*)p.A, ok);
+        const bool ok = a_row_ok[j] && k_ok;
+        cp_async16(dst + a_dst[j], ok ? (const void*)(a_src[j] + k0) : (const void*)p.A, ok);
       }
       cp_async_arrive(bar);
-      if (++stage == kStages) { stage = 0; phase ^= 1; }
+      dst += C::kStageBytes;
+      bar += 8;
+      if (++stage == kStages) { stage = 0; phase ^= 1; dst = smem_u32(smem); bar = full_w; }
     }
-    // the ring must be drained before the CTA's shared memory is given back: the last kStages
-    // "full" barriers complete only when their copies have landed
-    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == 1) {
     // ================================================================== MMA issuer
     if (lane == 0) {
@@ -260,7 +268,6 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       it.init(U0, U1, ups);
       int stage = 0, phase = 0, slot = 0, slot_phase = 0, seg = 0;
       for (; it.valid(); it.next()) {
-        const bool is6 = it.strip_lin >= geo.strips4;
         const int dbuf = seg & 1;
         const uint32_t d_tmem = tmem + (dbuf ? C::kTmemD1 : C::kTmemD0);
         const bool first = it.seg_first(U0);
@@ -274,7 +281,6 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         for (int st = 0; st < 4; ++st) {
           const uint64_t desc = act_desc(act + st * (NT / 8) * 256);
           tc_mma_ts(d_tmem, tmem + C::kTmemA + slot * 32 + st * 8, desc, C::kIdesc, (first && st == 0) ? 0u : 1u);
-          if (!is6) tc_mma_ts(d_tmem, tmem + C::kTmemBias, desc, C::kIdesc, 1u);
         }
         tc_commit(a_empty + 8 * slot);
         tc_commit(empty_w + 8 * stage);
@@ -292,12 +298,6 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
     const int c = quarter * 32 + lane;               // weight column inside the strip = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const int dtid = tid - 64;                       // 0..127 among the dequantiser threads
-    {
-      // constant operand tile that removes the 1024 / 64 offsets of the expanded INT4 nibbles
-      const uint32_t bias[8] = {kNegBiasLo, kNegBiasHi, kNegBiasLo, kNegBiasHi, kNegBiasLo, kNegBiasHi, kNegBiasLo, kNegBiasHi};
-      tc_st8(lane_base + C::kTmemBias, bias);
-      tc_wait_st();
-    }
     float acc[NT];
 #pragma unroll
     for (int m = 0; m < NT; ++m) acc[m] = 0.f;
@@ -426,15 +426,22 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
           float sum[NT];
 #pragma unroll
           for (int m = 0; m < NT; ++m) sum[m] = 0.f;
-          for (int cc = c_lo; cc <= c_hi; ++cc) {
-            if (p.sched.bound[cc] >= p.sched.bound[cc + 1]) continue;
-            const int cc_first = p.sched.bound[cc] / ups;
-            const float* src = p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
-            float v[NT];
+          constexpr int kBatch = NT <= 32 ? 2 : 1;   // slots whose loads are in flight together
+          for (int cbase = c_lo; cbase <= c_hi; cbase += kBatch) {
+            float v[kBatch][NT];
 #pragma unroll
-            for (int m = 0; m < NT; ++m) v[m] = __ldcg(src + m * kStripCols);
+            for (int i = 0; i < kBatch; ++i) {
+              const int cc = cbase + i;
+              const bool live = cc <= c_hi && p.sched.bound[cc] < p.sched.bound[cc + 1];
+              const int cc_first = live ? p.sched.bound[cc] / ups : 0;
+              const float* src = p.partials + (size_t)(2 * (live ? cc : cta) + (live && strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
 #pragma unroll
-            for (int m = 0; m < NT; ++m) sum[m] += v[m];
+              for (int m = 0; m < NT; ++m) v[i][m] = live ? __ldcg(src + m * kStripCols) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+              for (int m = 0; m < NT; ++m) sum[m] += v[i][m];
           }
           if (writes) {
 #pragma unroll
