@@ -33,6 +33,8 @@ SIGNATURES = {
     "fp6m_mul_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "fp6m_mul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp, _sz, _i, _vp,
                       _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "fp6m_mul_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _i, _vp,
+                                     _i, _i, _i, _i, _i, _i, _i, _vp]),
     "fp6m_dump_operands": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "fp6m_last_cuda_error": (ctypes.c_char_p, []),
     "fp6m_version": (ctypes.c_char_p, []),

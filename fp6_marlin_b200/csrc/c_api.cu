@@ -120,6 +120,29 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   return FP6M_OK;
 }
 
+// Scratch of fp6m_mul_static_scratch.  In host code this name is only a handle: the device address
+// comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_static_scratch[FP6M_STATIC_SCRATCH_BYTES];
+
+int fp6m_mul_static_scratch(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+                            void* workspace, size_t workspace_bytes, int dev, void* stream,
+                            int thread_k, int thread_n, int sms, int max_par,
+                            int quant_cols, int group_size, int layout, int* status_dev) {
+  static void* scratch_of_device[64] = {};
+  if (dev < 0 || dev >= 64) return FP6M_ERR_BAD_ARG;
+  if (!scratch_of_device[dev]) {
+    DeviceGuard guard(dev);                 // the symbol has one instance per device: ask with `dev` current
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+    scratch_of_device[dev] = ptr;
+  }
+  // fp6m_mul checks the size it needs against what it is given and returns FP6M_ERR_SCRATCH if it is short
+  return fp6m_mul(A, B, C, s, M, N, K, workspace, workspace_bytes, scratch_of_device[dev],
+                  (size_t)FP6M_STATIC_SCRATCH_BYTES, dev, stream, thread_k, thread_n, sms, max_par,
+                  quant_cols, group_size, layout, status_dev);
+}
+
 int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, int quant_cols,
                        int group_size, int dev, void* stream) {
   if (!B || !s || !W_out || N <= 0 || K <= 0) return FP6M_ERR_BAD_ARG;

@@ -109,6 +109,25 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
              int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
              int quant_cols, int group_size, int layout, int* status_dev);
 
+/* Same GEMM as fp6m_mul for callers that may not allocate device memory at all: plug-ins living
+ * inside a host runtime that owns the whole memory arena, code running after an allocator freeze
+ * or while other threads hold the device in a state where cudaMalloc's implicit synchronisation is
+ * not acceptable.  The split-K scratch is a static array inside the library (FP6M_STATIC_SCRATCH_BYTES,
+ * 8 MiB, resident on every GPU that loads the library until the process exits); the caller still
+ * passes A, B, C, s and the workspace.  This entry point has no counterpart in the reference.
+ *   - Enough for up to 16 rows of A per call on any grid (larger M fits when `sms` limits the grid);
+ *     a call that would need more returns FP6M_ERR_SCRATCH and launches nothing.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress); make
+ *     that first call outside any stream capture.
+ *   - All calls share the one array: calls that can overlap on the GPU (different streams) race.
+ *     Nothing in it has to be zero between calls.
+ *   - Never calls cudaMalloc, cudaFree or any allocating routine. */
+#define FP6M_STATIC_SCRATCH_BYTES (8u << 20)
+int fp6m_mul_static_scratch(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+                            void* workspace, size_t workspace_bytes, int dev, void* stream,
+                            int thread_k, int thread_n, int sms, int max_par,
+                            int quant_cols, int group_size, int layout, int* status_dev);
+
 /* Debug: the fp16 operand tile the kernels feed the tensor cores, W_deq[K, N] row-major, produced by
  * the same device dequantisation routines.  Lets a test prove bit-exactness against the reference
  * dequantisers (dequant_8int4 / dequant_8fp6, fp6_marlin_cuda_kernel.cu:195-286). */
