@@ -215,20 +215,12 @@ def reference_arm(args):
 # ------------------------------------------------------------------------------------------------
 # the B200 arm
 # ------------------------------------------------------------------------------------------------
-def shard_columns(w, rank: int, world: int):
-    """Columns of rank `rank`: its slice of the INT4 columns followed by its slice of the FP6 columns."""
-    import torch
-    n4 = N_DIM - QUANT_COLS
-    a, b = n4 // world, QUANT_COLS // world
-    return torch.cat([w[:, rank * a:(rank + 1) * a], w[:, n4 + rank * b: n4 + (rank + 1) * b]], dim=1).contiguous()
-
-
 def b200_arm(args):
     import torch
     import torch.distributed as dist
 
     import fp6_marlin_b200 as fm
-    from fp6_marlin_b200 import synth
+    from fp6_marlin_b200 import shard, synth
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -243,7 +235,7 @@ def b200_arm(args):
     n_local, qc_local = N_DIM // world, QUANT_COLS // world
     w = synth.make_weight_fp16(K_DIM, N_DIM, QUANT_COLS, seed=0)
     if world > 1:
-        w = shard_columns(w, rank, world)
+        w = shard.shard_weight(w, shard.ShardPlan(N_DIM, QUANT_COLS, world), rank)
     weight = fm.make_w46_weight(w, qc_local, GROUP, keep_dequantized=False, quant_device=dev)
     copies = [(weight.B.to(dev).clone(), weight.s.to(dev).clone()) for _ in range(WEIGHT_COPIES)]
     a_host = synth.make_activations(M_ROWS, K_DIM).pin_memory()
