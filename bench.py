@@ -237,7 +237,8 @@ def b200_arm(args):
     if world > 1:
         w = shard.shard_weight(w, shard.ShardPlan(N_DIM, QUANT_COLS, world), rank)
     weight = fm.make_w46_weight(w, qc_local, GROUP, keep_dequantized=False, quant_device=dev)
-    copies = [(weight.B.to(dev).clone(), weight.s.to(dev).clone()) for _ in range(WEIGHT_COPIES)]
+    n_copies = max(WEIGHT_COPIES, int(280e6 // (weight.B.numel() * 4)) + 1)      # > 2 x L2 in total
+    copies = [(weight.B.to(dev).clone(), weight.s.to(dev).clone()) for _ in range(n_copies)]
     a_host = synth.make_activations(M_ROWS, K_DIM).pin_memory()
     a_dev = a_host.to(dev)
     c_dev = torch.zeros((M_ROWS, n_local), dtype=torch.float16, device=dev)
@@ -247,7 +248,7 @@ def b200_arm(args):
     stream = torch.cuda.Stream(device=dev)
 
     def step(i, a):
-        B, s = copies[i % WEIGHT_COPIES]
+        B, s = copies[i % n_copies]
         fm.mul(a, B, c_dev, s, workspace, qc_local, group_size=GROUP, layout="b200")
         if world > 1:
             dist.all_gather_into_tensor(gathered, c_dev)
@@ -267,7 +268,7 @@ def b200_arm(args):
         # ---- value: K steps, captured in CUDA graphs when single-GPU
         chunk = min(GRAPH_CHUNK, args.steps)
         graphs = []
-        if world == 1:
+        if True:
             for count in ([chunk] if args.steps % chunk == 0 else [chunk, args.steps % chunk]):
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=stream):
@@ -278,14 +279,10 @@ def b200_arm(args):
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
-        if world == 1:
-            for _ in range(args.steps // chunk):
-                graphs[0][0].replay()
-            if args.steps % chunk:
-                graphs[1][0].replay()
-        else:
-            for i in range(args.steps):
-                step(i, a_dev)
+        for _ in range(args.steps // chunk):
+            graphs[0][0].replay()
+        if args.steps % chunk:
+            graphs[1][0].replay()
         ev1.record(stream)
         barrier()
         ms_total = ev0.elapsed_time(ev1)
@@ -330,9 +327,9 @@ def b200_arm(args):
         "data": "synthetic",
         "config": {"workload": "cfg1 square layer K=N=8192 M=16 qc=256 INT4-g128", "M": M_ROWS, "K": K_DIM, "N": N_DIM,
                    "quant_cols": QUANT_COLS, "group_size": GROUP,
-                   "l2": f"{WEIGHT_COPIES} rotating weight copies ({WEIGHT_COPIES * weight.B.numel() * 4 / 1e6:.0f} MB) exceed L2",
+                   "l2": f"{n_copies} rotating weight copies ({n_copies * weight.B.numel() * 4 / 1e6:.0f} MB) exceed L2",
                    "parallelism": "single GPU" if world == 1 else f"N-sharded over {world} GPUs + NCCL all-gather of output columns",
-                   "graph": world == 1},
+                   "graph": True},
         "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": M_ROWS * N_DIM * 2},
         "gpu_launches": args.steps,
@@ -352,7 +349,15 @@ def b200_arm(args):
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        # CUDA graphs that captured NCCL work must go before the communicator does; a watchdog ends the
+        # process if the tear-down of the process group stalls (the result line is already printed)
+        graphs.clear()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        threading.Timer(20.0, lambda: os._exit(0)).start()
+        dist.barrier()
         dist.destroy_process_group()
+        os._exit(0)
 
 
 def read_traffic_from_profile():
