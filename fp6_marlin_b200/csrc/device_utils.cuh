@@ -75,12 +75,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, bool& dead) {
+  // fast path: one potentially-blocking try_wait; in steady state the phase is complete already
+  if (mbar_try_wait(bar, parity)) return;
   if (dead) return;
-  if (mbar_test_wait(bar, parity)) return;
-  // a short tight poll (lowest wake-up latency), then parked waits
-#pragma unroll 1
-  for (int i = 0; i < 4096; ++i)
-    if (mbar_test_wait(bar, parity)) return;
+  // try_wait parks the thread in hardware until the phase completes or the hint elapses, so waiting
+  // roles put no polling traffic on the shared-memory pipeline that the working warps also use
 #pragma unroll 1
   for (int i = 0; i < (1 << 16); ++i)
     if (mbar_try_wait_hint(bar, parity, 16384u)) return;     // up to 65536 x 16 us

@@ -6,22 +6,24 @@
 // MEMORY, so they never travel through shared memory.  Legacy mma.sync costs about 32 cycles per
 // m16n8k16 tile on B200 and cannot keep up with HBM (profiles/w46_gemm_mma_*); tcgen05 can.
 //
-// One CTA = six warps:
-//   warp 0      producer: bulk TMA copies (cp.async.bulk, mbarrier completion) of one 64-row unit
-//               of packed words and its group scales per stage, plus cp.async copies that lay the
-//               unit's activations out as canonical K-major 8x16-byte core matrices.
+// One CTA = seven warps:
+//   warp 0      weights producer: one bulk TMA copy (cp.async.bulk, mbarrier completion) per
+//               SEGMENT = the one or two 64-row units of a 128-row block that belong to the CTA.
+//   warp 6      activations producer: cp.async copies that lay the segment's activations out as
+//               canonical K-major 8x16-byte core matrices (the B operand of the MMA).
 //   warp 1      one lane issues tcgen05.mma (kind::f16, fp32 accumulators in TMEM) and commits
 //               completion to mbarriers; the warp also owns the TMEM allocation.
 //   warps 2-5   dequantisers: thread = weight column = TMEM lane.  A thread reads its 32 bytes of
 //               a unit, expands the eight words in registers and stores them with tcgen05.st into
-//               a small TMEM operand ring.  INT4 nibbles become the exact integers q - 8 in fp16
+//               a ring of TMEM operand slots.  INT4 nibbles become the exact integers q - 8 in fp16
 //               (OR into 1024 + q / 64 + q, then subtract 1032 / 72) - bit for bit what the
 //               reference's dequant_8int4 feeds its tensor cores (fp6_marlin_cuda_kernel.cu:249-286).
 //               FP6 codes become `s 00eee mm` fp16 patterns (exact value / 4096, as dequant_8fp6
 //               builds them before its multiply by 4096, :195-237).  After every scale
 //               group (128 rows) the same threads read the accumulator tile back (tcgen05.ld),
-//               multiply by their column's group scale in fp32 and add to registers; two accumulator
-//               tiles alternate so the read-back overlaps the next group's MMAs.
+//               multiply by their column's group scale in fp32 and add to registers; every ring
+//               position has its own accumulator tile and the read-back runs one or two segments
+//               late, so it never waits for the tensor core.
 // Work comes from the byte-weighted stripe schedule (fp6m_layout.h); strips shared by several CTAs
 // are reduced through fp32 scratch slots by the last CTA to arrive (one acq_rel atomic on a counter
 // in the caller's workspace) - no CTA waits for another, every wait in the kernel is bounded.
@@ -38,26 +40,23 @@ namespace fp6m {
 
 namespace {
 
-constexpr int kThreads = 192;
-constexpr int kDequantThreads = 128;
-constexpr int kUnitW = 6144;            // packed words of one unit: up to 4096 four-bit + 2048 two-bit
-constexpr int kUnitS = 256;             // group scales of the unit's block: 128 fp16
-constexpr int kActOffset = kUnitW + kUnitS;
-constexpr int kTmemSlots = 3;           // operand ring: 3 units x 4 K-steps x 8 columns
+constexpr int kThreads = 384;          // 12 warps: W producer, MMA, A producer, (idle), 2 x 4 dequantisers
+constexpr int kDequantThreads = 256;
+constexpr int kStageW = 12288;          // packed words of one block: up to 2 x (4096 four-bit + 2048 two-bit)
 
-template <int NT_, int STAGES_, int CTAS_PER_SM_>
+template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_>
 struct Tc5Cfg {
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
-  static constexpr int kStages = STAGES_;
+  static constexpr int kStages = STAGES_;              // shared-memory stages of packed words (one block each)
+  static constexpr int kRing = RING_;                  // ring of {activation tile, TMEM operand slot, accumulator tile}
   static constexpr int kCtasPerSm = CTAS_PER_SM_;
-  static constexpr int kActBytes = NT * 128;           // NT rows x 64 halves
-  static constexpr int kStageBytes = kActOffset + kActBytes;
-  static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kNumBars = 2 * kStages + 2 * kTmemSlots + 4;
-  static constexpr int kSmemBytes = kRingBytes + kNumBars * 8 + 64;
-  static constexpr int kTmemD0 = 0, kTmemD1 = NT, kTmemA = 2 * NT;
-  static constexpr int kTmemUsed = kTmemA + kTmemSlots * 32;
-  static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : 256;
+  static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves
+  static constexpr int kActBytes = 2 * kActUnitBytes;
+  static constexpr int kNumBars = 2 * kStages + 3 * kRing;
+  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kNumBars * 8 + 64;
+  static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
+  static constexpr int kTmemUsed = kTmemA + kRing * 64;
+  static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
   static constexpr int kSlotFloats = NT * kStripCols;
   static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 };
@@ -96,6 +95,15 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
   tc_wait_ld();
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 // 16-byte asynchronous copy with zero fill when `valid` is false; completion is reported to an
 // mbarrier by cp_async_arrive below.
@@ -136,36 +144,40 @@ __device__ __forceinline__ void expand_fp6(uint32_t four, uint32_t two, int rot,
   b[3] = prmt(x1, 0u, 0x3424u);
 }
 
-// Walks the units [u0, u1) of a CTA; every role runs the same walk, so stage, slot and segment
-// numbers agree without communication.  A SEGMENT is a run of units inside one block and one strip.
-struct UnitIter {
+// Walks the units [u0, u1) of a CTA as SEGMENTS: runs of one or two units inside one 128-row block
+// of one strip (= one INT4 scale group, one TMA copy, one operand slot, one accumulator tile).
+// Every role runs the same walk, so ring positions agree without communication.
+struct Walk {
   int u, end, ups;
-  int strip_lin, unit;        // unit = index inside the strip
+  int unit, unit1;                 // position inside the strip, end of this CTA's slice of the strip
+  __device__ __forceinline__ void open_slice() { unit1 = min(ups, unit + end - u); }
   __device__ __forceinline__ void init(int u0, int u1, int ups_) {
     u = u0; end = u1; ups = ups_;
-    strip_lin = u / ups;
-    unit = u - strip_lin * ups;
+    unit = u % ups;
+    open_slice();
   }
   __device__ __forceinline__ bool valid() const { return u < end; }
-  __device__ __forceinline__ bool slice_first(int u0) const { return u == u0 || unit == 0; }
-  __device__ __forceinline__ bool slice_last() const { return u + 1 == end || unit + 1 == ups; }
-  __device__ __forceinline__ bool seg_first(int u0) const { return slice_first(u0) || (unit & 1) == 0; }
-  __device__ __forceinline__ bool seg_last() const { return slice_last() || (unit & 1) == 1; }
-  __device__ __forceinline__ void next() {
-    ++u;
-    if (++unit == ups) { unit = 0; ++strip_lin; }
+  __device__ __forceinline__ int count() const { return ((unit & 1) == 0 && unit + 1 < unit1) ? 2 : 1; }
+  // returns true when the step left the strip
+  __device__ __forceinline__ bool next(int cnt) {
+    u += cnt;
+    unit += cnt;
+    if (unit != ups) return false;
+    unit = 0;
+    open_slice();
+    return true;
   }
 };
 
 template <class C>
 __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(const __grid_constant__ MulParams p) {
-  constexpr int NT = C::NT, kStages = C::kStages;
+  constexpr int NT = C::NT, S = C::kStages, R = C::kRing;
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kRingBytes);
-  uint32_t* misc = reinterpret_cast<uint32_t*>(smem + C::kRingBytes + C::kNumBars * 8);   // [0] TMEM base, [1] flag
-  const uint32_t full_w = smem_u32(bars), empty_w = full_w + 8 * kStages;
-  const uint32_t a_full = empty_w + 8 * kStages, a_empty = a_full + 8 * kTmemSlots;
-  const uint32_t d_full = a_empty + 8 * kTmemSlots, d_empty = d_full + 16;
+  uint8_t* act_base = smem + S * kStageW;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kStageW + R * C::kActBytes);
+  uint32_t* misc = reinterpret_cast<uint32_t*>(bars + C::kNumBars);   // [0] TMEM base, [1] flag
+  const uint32_t w_full = smem_u32(bars), w_empty = w_full + 8 * S;
+  const uint32_t act_full = w_empty + 8 * S, ready = act_full + 8 * R, done = ready + 8 * R;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x;
@@ -175,17 +187,14 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   if (U0 >= U1) return;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_w + 8 * s, 33);     // the expect_tx arrival + 32 lanes of cp.async completions
-      mbar_init(empty_w + 8 * s, 5);     // four dequantiser warps + the MMA commit
+    for (int s = 0; s < S; ++s) {
+      mbar_init(w_full + 8 * s, 1);      // the expect_tx arrival of the weights producer
+      mbar_init(w_empty + 8 * s, 8);     // eight dequantiser warps have the words in registers
     }
-    for (int t = 0; t < kTmemSlots; ++t) {
-      mbar_init(a_full + 8 * t, 4);
-      mbar_init(a_empty + 8 * t, 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(d_full + 8 * b, 1);
-      mbar_init(d_empty + 8 * b, 4);
+    for (int r = 0; r < R; ++r) {
+      mbar_init(act_full + 8 * r, 32);   // cp.async completions of the 32 lanes of the activation producer
+      mbar_init(ready + 8 * r, 8);       // eight dequantiser warps stored the operands into TMEM
+      mbar_init(done + 8 * r, 1);        // tcgen05.commit: every MMA of the segment has finished
     }
     mbar_fence_init();
   }
@@ -200,194 +209,229 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   bool dead = false;
 
   if (warp == 0) {
-    // ================================================================== producer
-    const uint64_t policy = make_evict_first_policy();
-    UnitIter it;
-    it.init(U0, U1, ups);
-    int stage = 0, phase = 0;
-    int cur_strip = -1, nq = 0;
-    bool group = false;
-    const uint8_t* wsrc = nullptr;      // next unit's packed words
-    const half* ssrc = nullptr;         // group scales of the strip's first block
-    uint32_t unit_bytes = 0, sbytes = 0;
-    // activations: this lane copies chunks idx = lane + 32 j: row m = idx / 8, 16-byte chunk kc = idx % 8
-    // of the unit, into canonical core-matrix order; everything but the K offset is loop-invariant
-    const half* a_src[NT / 4];
-    uint32_t a_dst[NT / 4];
-    bool a_row_ok[NT / 4];
-    const int kc = lane & 7;
-#pragma unroll
-    for (int j = 0; j < NT / 4; ++j) {
-      const int m = (lane >> 3) + 4 * j;
-      a_row_ok[j] = m < p.M;
-      a_src[j] = p.A + (size_t)(a_row_ok[j] ? m : 0) * p.K + 8 * kc;
-      a_dst[j] = kActOffset + (kc >> 1) * (NT / 8) * 256 + ((m >> 3) * 2 + (kc & 1)) * 128 + (m & 7) * 16;
-    }
-    uint32_t dst = smem_u32(smem), bar = full_w;
-    for (; it.valid(); it.next()) {
-      if (it.strip_lin != cur_strip) {
-        cur_strip = it.strip_lin;
-        const bool is6 = cur_strip >= geo.strips4;
-        if (!is6) {
-          nq = strip_quads(geo.n4, cur_strip);
-          unit_bytes = nq * kInt4UnitQuadBytes;
-          wsrc = p.B + int4_unit_offset(geo, cur_strip, 0) + (size_t)it.unit * unit_bytes;
-          group = geo.groups > 1;
-          ssrc = p.S + int4_scale_offset(geo, cur_strip, 0);
-        } else {
-          nq = strip_quads(geo.n6, cur_strip - geo.strips4);
-          unit_bytes = nq * kFp6UnitQuadBytes;
-          wsrc = p.B + fp6_unit_offset(geo, cur_strip - geo.strips4, 0) + (size_t)it.unit * unit_bytes;
-          group = false;
+    // ================================================================== weights producer
+    if (lane == 0) {
+      const uint64_t policy = make_evict_first_policy();
+      Walk it;
+      it.init(U0, U1, ups);
+      bool new_strip = true;
+      int strip_lin = U0 / ups;
+      const uint8_t* wsrc = nullptr;
+      uint32_t unit_bytes = 0;
+      uint32_t dst = smem_u32(smem), full = w_full, empty = w_empty;
+      int stage = 0;
+      uint32_t phase = 0;
+      while (it.valid()) {
+        if (new_strip) {
+          if (strip_lin < geo.strips4) {
+            unit_bytes = strip_quads(geo.n4, strip_lin) * kInt4UnitQuadBytes;
+            wsrc = p.B + int4_unit_offset(geo, strip_lin, 0) + (size_t)it.unit * unit_bytes;
+          } else {
+            unit_bytes = strip_quads(geo.n6, strip_lin - geo.strips4) * kFp6UnitQuadBytes;
+            wsrc = p.B + fp6_unit_offset(geo, strip_lin - geo.strips4, 0) + (size_t)it.unit * unit_bytes;
+          }
         }
-        sbytes = group ? nq * 64 : 0;
+        const int cnt = it.count();
+        mbar_wait_bounded(empty, phase ^ 1, p.status, dead);
+        const uint32_t bytes = cnt * unit_bytes;            // consecutive units are contiguous in HBM
+        mbar_arrive_expect_tx(full, bytes);
+        tma_load_1d_stream(dst, wsrc, bytes, full, policy);
+        wsrc += bytes;
+        dst += kStageW; full += 8; empty += 8;
+        if (++stage == S) { stage = 0; phase ^= 1; dst = smem_u32(smem); full = w_full; empty = w_empty; }
+        new_strip = it.next(cnt);
+        strip_lin += new_strip;
       }
-      mbar_wait_bounded(empty_w + 8 * stage, phase ^ 1, p.status, dead);
-      if (lane == 0) {
-        mbar_arrive_expect_tx(bar, unit_bytes + sbytes);
-        tma_load_1d_stream(dst, wsrc, unit_bytes, bar, policy);
-        if (group) tma_load_1d(dst + kUnitW, ssrc + (it.unit >> 1) * nq * kQuadCols, sbytes, bar);
-      }
-      wsrc += unit_bytes;
-      const int k0 = it.unit * kUnitRows;
-      const bool k_ok = k0 + 8 * kc < p.K;
-#pragma unroll
-      for (int j = 0; j < NT / 4; ++j) {
-        const bool ok = a_row_ok[j] && k_ok;
-        cp_async16(dst + a_dst[j], ok ? (const void*)(a_src[j] + k0) : (const void*)p.A, ok);
-      }
-      cp_async_arrive(bar);
-      dst += C::kStageBytes;
-      bar += 8;
-      if (++stage == kStages) { stage = 0; phase ^= 1; dst = smem_u32(smem); bar = full_w; }
     }
+  } else if (warp == 2) {
+    // ================================================================== activations producer
+    // lane copies chunks idx = lane + 32 j of a unit: row m = idx / 8, 16-byte chunk kc = idx % 8,
+    // into canonical K-major core-matrix order; everything but the K offset is loop-invariant
+    const int kc = lane & 7, m0 = lane >> 3;          // rows m = m0 + 4 j
+    const half* a_src0 = p.A + (size_t)m0 * p.K + 8 * kc;
+    const uint32_t a_dst0 = smem_u32(act_base) + (kc >> 1) * (NT / 8) * 256 + (kc & 1) * 128 + m0 * 16;
+    const size_t row4 = (size_t)4 * p.K;
+    Walk it;
+    it.init(U0, U1, ups);
+    int r = 0;
+    uint32_t rphase = 0;
+    while (it.valid()) {
+      const int cnt = it.count();
+      mbar_wait_bounded(done + 8 * r, rphase ^ 1, p.status, dead);     // the MMAs that read this tile are done
+      const uint32_t dst = a_dst0 + r * C::kActBytes;
+      for (int h = 0; h < cnt; ++h) {
+        const int k0 = (it.unit + h) * kUnitRows;
+        const bool k_ok = k0 + 8 * kc < p.K;
+        const half* src = a_src0 + k0;
+#pragma unroll
+        for (int j = 0; j < NT / 4; ++j) {
+          const bool ok = k_ok && m0 + 4 * j < p.M;
+          // row m: 8-row group m / 8 = j / 2 (256 bytes apart), row in group m % 8 = m0 + 4 (j % 2)
+          cp_async16(dst + h * C::kActUnitBytes + (j >> 1) * 256 + (j & 1) * 64, ok ? (const void*)(src + j * row4) : (const void*)p.A, ok);
+        }
+      }
+      cp_async_arrive(act_full + 8 * r);
+      if (++r == R) { r = 0; rphase ^= 1; }
+      it.next(cnt);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == 1) {
     // ================================================================== MMA issuer
     if (lane == 0) {
-      UnitIter it;
+      Walk it;
       it.init(U0, U1, ups);
-      int stage = 0, phase = 0, slot = 0, slot_phase = 0, seg = 0;
-      for (; it.valid(); it.next()) {
-        const int dbuf = seg & 1;
-        const uint32_t d_tmem = tmem + (dbuf ? C::kTmemD1 : C::kTmemD0);
-        const bool first = it.seg_first(U0);
-        mbar_wait_bounded(full_w + 8 * stage, phase, p.status, dead);
+      int r = 0;
+      uint32_t rphase = 0;
+      const uint64_t desc0 = act_desc(smem_u32(act_base));
+      while (it.valid()) {
+        const int cnt = it.count();
+        mbar_wait_bounded(act_full + 8 * r, rphase, p.status, dead);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
-        mbar_wait_bounded(a_full + 8 * slot, slot_phase, p.status, dead);
-        if (first) mbar_wait_bounded(d_empty + 8 * dbuf, ((seg >> 1) & 1) ^ 1, p.status, dead);
+        mbar_wait_bounded(ready + 8 * r, rphase, p.status, dead);
         tc_fence_after();
-        const uint32_t act = smem_u32(smem + stage * C::kStageBytes + kActOffset);
+        const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
+        const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
+        // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
+        const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
+        constexpr uint32_t kStepDesc = ((NT / 8) * 256) >> 4;
 #pragma unroll
-        for (int st = 0; st < 4; ++st) {
-          const uint64_t desc = act_desc(act + st * (NT / 8) * 256);
-          tc_mma_ts(d_tmem, tmem + C::kTmemA + slot * 32 + st * 8, desc, C::kIdesc, (first && st == 0) ? 0u : 1u);
+        for (int st = 0; st < 4; ++st) tc_mma_ts(d_tmem, a_tmem + st * 8, desc + st * kStepDesc, C::kIdesc, st != 0);
+        if (cnt == 2) {
+#pragma unroll
+          for (int st = 4; st < 8; ++st) tc_mma_ts(d_tmem, a_tmem + st * 8, desc + st * kStepDesc, C::kIdesc, 1);
         }
-        tc_commit(a_empty + 8 * slot);
-        tc_commit(empty_w + 8 * stage);
-        if (it.seg_last()) {
-          tc_commit(d_full + 8 * dbuf);
-          ++seg;
-        }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
-        if (++slot == kTmemSlots) { slot = 0; slot_phase ^= 1; }
+        tc_commit(done + 8 * r);
+        if (++r == R) { r = 0; rphase ^= 1; }
+        it.next(cnt);
       }
     }
-  } else {
-    // ================================================================== dequantisers (warps 2..5)
+  } else if (warp >= 4) {
+    // ================================================================== dequantisers (warps 4..11)
+    // Two teams of four warps.  Team t expands unit t of every segment (64 rows of the block) and reads
+    // back rows [t NT/2, (t+1) NT/2) of the accumulator tile, so each thread owns one weight column
+    // and half of the rows of A from the first load to the store of C.
+    constexpr int HN = NT / 2;
+    constexpr int DEFER = R - 1;                     // accumulator tiles are read back this many segments late
+    const int team = (warp - 4) >> 2;
     const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
     const int c = quarter * 32 + lane;               // weight column inside the strip = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    const int dtid = tid - 64;                       // 0..127 among the dequantiser threads
-    float acc[NT];
+    const uint32_t d_base = lane_base + C::kTmemD + team * HN;     // + r * NT
+    const uint32_t a_base = lane_base + C::kTmemA + team * 32;     // + r * 64
+    const int dtid = tid - 128;                      // 0..255 among the dequantiser threads
+    const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16
+    float acc[HN];
 #pragma unroll
-    for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+    for (int m = 0; m < HN; ++m) acc[m] = 0.f;
 
-    UnitIter it;
-    it.init(U0, U1, ups);
-    int stage = 0, phase = 0, slot = 0, slot_phase = 0, seg = 0;
-    const int strip_first = it.strip_lin;
-    bool pending = false;          // a finished segment whose accumulator tile is not read back yet
-    int pend_seg = 0;
-    float pend_scale = 1.f;
+    // ring positions run on across slices
+    int stage = 0, r = 0, rb = 0;                    // weights stage, ring entry to fill, ring entry to read back
+    uint32_t wphase = 0, rbphase = 0;
+    const int strip_first = U0 / ups;
+    int strip_lin = strip_first;
+    int u = U0;
 
-    auto read_back = [&]() {
-      const int dbuf = pend_seg & 1;
-      mbar_wait_bounded(d_full + 8 * dbuf, (pend_seg >> 1) & 1, p.status, dead);
-      tc_fence_after();
-      const uint32_t d_tmem = lane_base + (dbuf ? C::kTmemD1 : C::kTmemD0);
-#pragma unroll
-      for (int m0 = 0; m0 < NT; m0 += 16) {
-        float d[16];
-        tc_ld16(d_tmem + m0, d);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[m0 + i] = fmaf(pend_scale, d[i], acc[m0 + i]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(d_empty + 8 * dbuf);
-      pending = false;
-    };
-
-    while (it.valid()) {
+    while (u < U1) {
       // ---------------- one slice: this CTA's units of one strip
-      const int strip_lin = it.strip_lin;
       const bool is6 = strip_lin >= geo.strips4;
       const int strip = is6 ? strip_lin - geo.strips4 : strip_lin;
       const int nq = strip_quads(is6 ? geo.n6 : geo.n4, strip);
       const bool group = !is6 && geo.groups > 1;
       const bool col_live = c < nq * kQuadCols;       // padded quads of a ragged strip hold no data
-      const int swz = (c >> 2) & 1;
+      const uint32_t unit_bytes = nq * (is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
       const int s_begin = strip_lin * ups, s_end = s_begin + ups;
-      const int slice_u0 = it.u;
-      float seg_scale = 1.f;
+      const int slice_u0 = u;
+      const int slice_u1 = min(U1, s_end);
+      int unit = u - s_begin;
+      const int unit1 = slice_u1 - s_begin;
+      const uint32_t my_off = team * unit_bytes + lds_lo;
+      const uint32_t two_off = team * unit_bytes + nq * kInt4UnitQuadBytes + c * 16;
+      const int scale_stride = nq * kQuadCols;
+      const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.S) +
+                                 (group ? int4_scale_offset(geo, strip, 0) + c + (size_t)(unit >> 1) * scale_stride : 0);
+      int npend = 0;                                   // segments whose accumulator tile is not read back yet
+      float pend[DEFER];                               // their group scales, oldest first
+#pragma unroll
+      for (int i = 0; i < DEFER; ++i) pend[i] = 1.f;
 
-      while (it.valid() && it.strip_lin == strip_lin) {
-        mbar_wait_bounded(full_w + 8 * stage, phase, p.status, dead);
-        const uint8_t* st = smem + stage * C::kStageBytes;
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, two = lo;
-        if (col_live) {
-          lo = *reinterpret_cast<const uint4*>(st + c * 32 + 16 * swz);          // words 0..3
-          hi = *reinterpret_cast<const uint4*>(st + c * 32 + 16 * (swz ^ 1));    // words 4..7
-          if (is6) two = *reinterpret_cast<const uint4*>(st + nq * kInt4UnitQuadBytes + c * 16);
-          if (group && it.seg_first(U0)) seg_scale = __half2float(*reinterpret_cast<const half*>(st + kUnitW + c * 2));
+      auto read_back_oldest = [&]() {
+        mbar_wait_bounded(done + 8 * rb, rbphase, p.status, dead);
+        tc_fence_after();
+        const float scale = pend[0];
+        const uint32_t d_tmem = d_base + rb * NT;
+        if (HN == 8) {
+          float d[8];
+          tc_ld8(d_tmem, d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(scale, d[i], acc[i]);
+        } else {
+#pragma unroll
+          for (int m0 = 0; m0 < HN; m0 += 16) {
+            float d[16];
+            tc_ld16(d_tmem + m0, d);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[(m0 + i) % HN] = fmaf(scale, d[i], acc[(m0 + i) % HN]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i + 1 < DEFER; ++i) pend[i] = pend[i + 1];
+        if (++rb == R) { rb = 0; rbphase ^= 1; }
+        --npend;
+      };
+
+      while (unit < unit1) {
+        const int cnt = ((unit & 1) == 0 && unit + 1 < unit1) ? 2 : 1;
+        // 1.0 unless the strip has group scales; converted only when queued, so the load's latency is hidden
+        unsigned short scale_raw = 0x3C00;
+        if (group && col_live) scale_raw = __ldg(sp);
+        sp += scale_stride;
+        mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
+        const bool mine = team < cnt;                 // this team's unit exists in the segment
+        if (mine) {
+          const uint8_t* st = smem + stage * kStageW;
+          uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, two = lo;
+          if (col_live) {
+            lo = *reinterpret_cast<const uint4*>(st + my_off);          // words 0..3
+            hi = *reinterpret_cast<const uint4*>(st + (my_off ^ 16));   // words 4..7
+            if (is6) two = *reinterpret_cast<const uint4*>(st + two_off);
+          }
+          // The operand slot and the accumulator tile of ring entry r were last used R segments ago;
+          // that segment was read back (after a wait on its `done`) before this point in program order.
+          const uint32_t a_tmem = a_base + r * 64;
+          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
+#pragma unroll
+          for (int step = 0; step < 4; ++step) {
+            uint32_t regs[8];
+            if (is6) {
+              expand_fp6(words[2 * step], twos[step], 0, regs);
+              expand_fp6(words[2 * step + 1], twos[step], 4, regs + 4);
+            } else {
+              expand_int4(words[2 * step], regs);
+              expand_int4(words[2 * step + 1], regs + 4);
+            }
+            tc_st8(a_tmem + step * 8, regs);
+          }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_w + 8 * stage);          // the stage's words are in registers
-        mbar_wait_bounded(a_empty + 8 * slot, slot_phase ^ 1, p.status, dead);
-        tc_fence_after();
-        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
-        const uint32_t a_tmem = lane_base + C::kTmemA + slot * 32;
-#pragma unroll
-        for (int step = 0; step < 4; ++step) {
-          uint32_t r[8];
-          if (is6) {
-            expand_fp6(words[2 * step], twos[step], 0, r);
-            expand_fp6(words[2 * step + 1], twos[step], 4, r + 4);
-          } else {
-            expand_int4(words[2 * step], r);
-            expand_int4(words[2 * step + 1], r + 4);
-          }
-          tc_st8(a_tmem + step * 8, r);
-        }
+        if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
         tc_wait_st();
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(a_full + 8 * slot);
-        const bool seg_end = it.seg_last();
-        if (seg_end) {
-          if (pending) read_back();                   // the previous segment, one segment late
-          pending = true;
-          pend_seg = seg;
-          pend_scale = seg_scale;
-          ++seg;
+        if (lane == 0) mbar_arrive(ready + 8 * r);
+        if (npend == DEFER) read_back_oldest();       // segment n - DEFER: its MMAs finished long ago
+        {
+          const float sc = __half2float(__ushort_as_half(scale_raw));
+#pragma unroll
+          for (int i = 0; i < DEFER; ++i)
+            if (npend == i) pend[i] = sc;
         }
-        it.next();
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
-        if (++slot == kTmemSlots) { slot = 0; slot_phase ^= 1; }
+        ++npend;
+        unit += cnt;
+        if (++stage == S) { stage = 0; wphase ^= 1; }
+        if (++r == R) r = 0;
       }
-      if (pending) read_back();
-      const int slice_u1 = it.valid() ? it.u : U1;
+      while (npend > 0) read_back_oldest();
+      u = slice_u1;
 
       // ---------------- the strip is finished for this CTA: write C, or publish a partial
       const bool full_strip = slice_u0 == s_begin && slice_u1 == s_end;
@@ -399,16 +443,17 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         const half* sp = p.S + (is6 ? fp6_scale_offset(geo, strip) : int4_scale_offset(geo, strip, 0));
         col_scale = __half2float(__ldg(sp + c)) * (is6 ? 4096.f : 1.f);
       }
+      const int row0 = team * HN;                    // this thread's rows of A and C
       if (full_strip) {
         if (writes) {
 #pragma unroll
-          for (int m = 0; m < NT; ++m)
-            if (m < p.M) p.C[(size_t)m * p.N + gcol] = __float2half_rn(acc[m] * col_scale);
+          for (int m = 0; m < HN; ++m)
+            if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(acc[m] * col_scale);
         }
       } else {
         float* slot_base = p.partials + (size_t)(2 * cta + (strip_lin != strip_first ? 1 : 0)) * C::kSlotFloats;
 #pragma unroll
-        for (int m = 0; m < NT; ++m) __stcg(slot_base + m * kStripCols + c, acc[m]);
+        for (int m = 0; m < HN; ++m) __stcg(slot_base + (row0 + m) * kStripCols + c, acc[m]);
         int c_lo = cta, c_hi = cta;
         while (c_lo > 0 && p.sched.bound[c_lo] > s_begin) --c_lo;
         while (c_hi + 1 < p.sched.ctas && p.sched.bound[c_hi + 1] < s_end) ++c_hi;
@@ -423,36 +468,37 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         named_bar_sync(1, kDequantThreads);
         if (misc[1] != 0) {
           // the last CTA to arrive sums the slots in CTA order (deterministic) and writes C
-          float sum[NT];
+          float sum[HN];
 #pragma unroll
-          for (int m = 0; m < NT; ++m) sum[m] = 0.f;
-          constexpr int kBatch = NT <= 32 ? 2 : 1;   // slots whose loads are in flight together
+          for (int m = 0; m < HN; ++m) sum[m] = 0.f;
+          constexpr int kBatch = HN <= 8 ? 4 : (HN <= 16 ? 2 : 1);   // slots whose loads are in flight together
           for (int cbase = c_lo; cbase <= c_hi; cbase += kBatch) {
-            float v[kBatch][NT];
+            float v[kBatch][HN];
 #pragma unroll
             for (int i = 0; i < kBatch; ++i) {
               const int cc = cbase + i;
               const bool live = cc <= c_hi && p.sched.bound[cc] < p.sched.bound[cc + 1];
               const int cc_first = live ? p.sched.bound[cc] / ups : 0;
-              const float* src = p.partials + (size_t)(2 * (live ? cc : cta) + (live && strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
+              const float* src = p.partials + (size_t)(2 * (live ? cc : cta) + (live && strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + row0 * kStripCols + c;
 #pragma unroll
-              for (int m = 0; m < NT; ++m) v[i][m] = live ? __ldcg(src + m * kStripCols) : 0.f;
+              for (int m = 0; m < HN; ++m) v[i][m] = live ? __ldcg(src + m * kStripCols) : 0.f;
             }
 #pragma unroll
             for (int i = 0; i < kBatch; ++i)
 #pragma unroll
-              for (int m = 0; m < NT; ++m) sum[m] += v[i][m];
+              for (int m = 0; m < HN; ++m) sum[m] += v[i][m];
           }
           if (writes) {
 #pragma unroll
-            for (int m = 0; m < NT; ++m)
-              if (m < p.M) p.C[(size_t)m * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
+            for (int m = 0; m < HN; ++m)
+              if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
           }
         }
         named_bar_sync(1, kDequantThreads);          // the flag may be rewritten by the next strip
       }
 #pragma unroll
-      for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+      for (int m = 0; m < HN; ++m) acc[m] = 0.f;
+      ++strip_lin;
     }
   }
 
@@ -464,9 +510,9 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   }
 }
 
-using Tc5Rows16 = Tc5Cfg<16, 8, 3>;
-using Tc5Rows32 = Tc5Cfg<32, 8, 2>;
-using Tc5Rows64 = Tc5Cfg<64, 6, 2>;
+using Tc5Rows16 = Tc5Cfg<16, 7, 3, 2>;
+using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2>;
+using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2>;
 
 template <class C>
 cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
