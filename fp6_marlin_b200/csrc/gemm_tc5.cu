@@ -44,16 +44,20 @@ constexpr int kThreads = 384;          // 12 warps: W producer, MMA, A producer,
 constexpr int kDequantThreads = 256;
 constexpr int kStageW = 12288;          // packed words of one block: up to 2 x (4096 four-bit + 2048 two-bit)
 
-template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_>
+template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_, bool ALT_>
 struct Tc5Cfg {
+  // ALT: the two dequantiser teams take alternate segments (two independent chains per CTA) and keep
+  // all NT rows in registers; otherwise both teams work on every segment (one unit, half of the rows each).
+  static constexpr bool kAlt = ALT_;
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kStages = STAGES_;              // shared-memory stages of packed words (one block each)
   static constexpr int kRing = RING_;                  // ring of {activation tile, TMEM operand slot, accumulator tile}
   static constexpr int kCtasPerSm = CTAS_PER_SM_;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves
   static constexpr int kActBytes = 2 * kActUnitBytes;
-  static constexpr int kNumBars = 2 * kStages + 3 * kRing;
-  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kNumBars * 8 + 64;
+  static constexpr int kNumBars = 2 * kStages + (ALT_ ? 4 : 3) * kRing;
+  static constexpr int kXchBytes = ALT_ ? NT * 128 * 4 : 0;   // the teams exchange half of their rows at the end of a slice
+  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kXchBytes + kNumBars * 8 + 64;
   static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
@@ -67,12 +71,31 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[128 x N] (+)= A[128 x 16] (TMEM) * B[N x 16]^T (shared memory descriptor)
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// The four MMAs of one 64-row unit, D[128 x N] (+)= A[128 x 16] (TMEM) * B[N x 16]^T (shared memory
+// descriptor) for K steps 0..3: the operand slot advances by 8 TMEM columns and the descriptor by
+// `step_desc` (16-byte units) per step.  `accumulate` = 0 makes the first MMA overwrite D.
+template <uint32_t kStepDesc>
+__device__ __forceinline__ void tc_mma_unit(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0)
+      "{\n"
+      ".reg .pred p, t;\n"
+      ".reg .b32 a1, a2, a3;\n"
+      ".reg .b64 d1, d2, d3;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "setp.eq.b32 t, 0, 0;\n"
+      "add.u32 a1, %1, 8;\n"
+      "add.u32 a2, %1, 16;\n"
+      "add.u32 a3, %1, 24;\n"
+      "add.u64 d1, %2, %5;\n"
+      "add.u64 d2, %2, %6;\n"
+      "add.u64 d3, %2, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], d1, %3, t;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], d2, %3, t;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], d3, %3, t;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate),
+        "n"(kStepDesc), "n"(2 * kStepDesc), "n"(3 * kStepDesc)
       : "memory");
 }
 // K-major, no swizzle: 8-row x 16-byte core matrices of 128 bytes; the two K halves of a step are
@@ -174,10 +197,12 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   constexpr int NT = C::NT, S = C::kStages, R = C::kRing;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* act_base = smem + S * kStageW;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kStageW + R * C::kActBytes);
+  float* xch = reinterpret_cast<float*>(smem + S * kStageW + R * C::kActBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kStageW + R * C::kActBytes + C::kXchBytes);
   uint32_t* misc = reinterpret_cast<uint32_t*>(bars + C::kNumBars);   // [0] TMEM base, [1] flag
   const uint32_t w_full = smem_u32(bars), w_empty = w_full + 8 * S;
   const uint32_t act_full = w_empty + 8 * S, ready = act_full + 8 * R, done = ready + 8 * R;
+  const uint32_t d_free = done + 8 * R;    // ALT only: the accumulator tile has been read back
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x;
@@ -189,11 +214,12 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(w_full + 8 * s, 1);      // the expect_tx arrival of the weights producer
-      mbar_init(w_empty + 8 * s, 8);     // eight dequantiser warps have the words in registers
+      mbar_init(w_empty + 8 * s, C::kAlt ? 4 : 8);   // the dequantiser warps that read the stage have its words in registers
     }
     for (int r = 0; r < R; ++r) {
       mbar_init(act_full + 8 * r, 32);   // cp.async completions of the 32 lanes of the activation producer
-      mbar_init(ready + 8 * r, 8);       // eight dequantiser warps stored the operands into TMEM
+      mbar_init(ready + 8 * r, C::kAlt ? 4 : 8);     // the dequantiser warps of the segment stored the operands into TMEM
+      if (C::kAlt) mbar_init(d_free + 8 * r, 4);     // the team that owns the segment has read the accumulator tile back
       mbar_init(done + 8 * r, 1);        // tcgen05.commit: every MMA of the segment has finished
     }
     mbar_fence_init();
@@ -275,230 +301,369 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       it.next(cnt);
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp == 1) {
-    // ================================================================== MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || (C::kAlt && warp == 3)) {
+    // ================================================================== MMA issuer(s)
+    // The whole warp walks the segments and waits (warp-uniform control flow and operands); one
+    // fixed lane issues the tcgen05 instructions, so that the commit tracks the MMAs before it.
+    // A single thread sustains about one small MMA per 75-120 cycles, the tensor core one per 32:
+    // with alternating teams each team has its own issuer (warp 1: even segments, warp 3: odd).
+    {
+      constexpr int kIssuers = C::kAlt ? 2 : 1;
+      const int mine = C::kAlt ? (warp == 3) : 0;
       Walk it;
       it.init(U0, U1, ups);
-      int r = 0;
+      int r = 0, n = 0;
       uint32_t rphase = 0;
       const uint64_t desc0 = act_desc(smem_u32(act_base));
+      constexpr uint32_t kStepDesc = ((NT / 8) * 256) >> 4;
       while (it.valid()) {
         const int cnt = it.count();
-        mbar_wait_bounded(act_full + 8 * r, rphase, p.status, dead);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
-        mbar_wait_bounded(ready + 8 * r, rphase, p.status, dead);
-        tc_fence_after();
-        const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
-        const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
-        // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
-        const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
-        constexpr uint32_t kStepDesc = ((NT / 8) * 256) >> 4;
-#pragma unroll
-        for (int st = 0; st < 4; ++st) tc_mma_ts(d_tmem, a_tmem + st * 8, desc + st * kStepDesc, C::kIdesc, st != 0);
-        if (cnt == 2) {
-#pragma unroll
-          for (int st = 4; st < 8; ++st) tc_mma_ts(d_tmem, a_tmem + st * 8, desc + st * kStepDesc, C::kIdesc, 1);
+        if (kIssuers == 1 || (n & 1) == mine) {
+          mbar_wait_bounded(act_full + 8 * r, rphase, p.status, dead);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
+          mbar_wait_bounded(ready + 8 * r, rphase, p.status, dead);
+          if (C::kAlt) mbar_wait_bounded(d_free + 8 * r, rphase ^ 1, p.status, dead);   // previous tile of this entry was read
+          tc_fence_after();
+          const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
+          const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
+          // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
+          const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
+          if (lane == 0) {
+            tc_mma_unit<kStepDesc>(d_tmem, a_tmem, desc, C::kIdesc, 0u);
+            if (cnt == 2) tc_mma_unit<kStepDesc>(d_tmem, a_tmem + 32, desc + 4 * kStepDesc, C::kIdesc, 1u);
+            tc_commit(done + 8 * r);
+          }
+          __syncwarp();
         }
-        tc_commit(done + 8 * r);
+        ++n;
         if (++r == R) { r = 0; rphase ^= 1; }
         it.next(cnt);
       }
     }
   } else if (warp >= 4) {
     // ================================================================== dequantisers (warps 4..11)
-    // Two teams of four warps.  Team t expands unit t of every segment (64 rows of the block) and reads
-    // back rows [t NT/2, (t+1) NT/2) of the accumulator tile, so each thread owns one weight column
-    // and half of the rows of A from the first load to the store of C.
+    // Two teams of four warps; thread = weight column = TMEM lane.  A thread owns half of the rows of
+    // A (rows [team NT/2, (team+1) NT/2)) when a slice is written out.
     constexpr int HN = NT / 2;
-    constexpr int DEFER = R - 1;                     // accumulator tiles are read back this many segments late
     const int team = (warp - 4) >> 2;
     const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
     const int c = quarter * 32 + lane;               // weight column inside the strip = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t d_base = lane_base + C::kTmemD + team * HN;     // + r * NT
-    const uint32_t a_base = lane_base + C::kTmemA + team * 32;     // + r * 64
     const int dtid = tid - 128;                      // 0..255 among the dequantiser threads
     const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16
-    float acc[HN];
-#pragma unroll
-    for (int m = 0; m < HN; ++m) acc[m] = 0.f;
-
-    // ring positions run on across slices
-    int stage = 0, r = 0, rb = 0;                    // weights stage, ring entry to fill, ring entry to read back
-    uint32_t wphase = 0, rbphase = 0;
     const int strip_first = U0 / ups;
-    int strip_lin = strip_first;
-    int u = U0;
+    const int row0 = team * HN;                      // this thread's rows of A and C
 
-    while (u < U1) {
-      // ---------------- one slice: this CTA's units of one strip
-      const bool is6 = strip_lin >= geo.strips4;
-      const int strip = is6 ? strip_lin - geo.strips4 : strip_lin;
-      const int nq = strip_quads(is6 ? geo.n6 : geo.n4, strip);
-      const bool group = !is6 && geo.groups > 1;
-      const bool col_live = c < nq * kQuadCols;       // padded quads of a ragged strip hold no data
-      const uint32_t unit_bytes = nq * (is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
-      const int s_begin = strip_lin * ups, s_end = s_begin + ups;
-      const int slice_u0 = u;
-      const int slice_u1 = min(U1, s_end);
-      int unit = u - s_begin;
-      const int unit1 = slice_u1 - s_begin;
-      const uint32_t my_off = team * unit_bytes + lds_lo;
-      const uint32_t two_off = team * unit_bytes + nq * kInt4UnitQuadBytes + c * 16;
-      const int scale_stride = nq * kQuadCols;
-      const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.S) +
-                                 (group ? int4_scale_offset(geo, strip, 0) + c + (size_t)(unit >> 1) * scale_stride : 0);
-      int npend = 0;                                   // segments whose accumulator tile is not read back yet
-      float pend[DEFER];                               // their group scales, oldest first
-#pragma unroll
-      for (int i = 0; i < DEFER; ++i) pend[i] = 1.f;
+    struct Slice {
+      int strip_lin, strip, nq, u0, u1, s_begin;
+      bool is6, group;
+    };
+    auto open_slice = [&](int strip_lin, int u) {
+      Slice sl;
+      sl.strip_lin = strip_lin;
+      sl.is6 = strip_lin >= geo.strips4;
+      sl.strip = sl.is6 ? strip_lin - geo.strips4 : strip_lin;
+      sl.nq = strip_quads(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      sl.group = !sl.is6 && geo.groups > 1;
+      sl.s_begin = strip_lin * ups;
+      sl.u0 = u;
+      sl.u1 = min(U1, sl.s_begin + ups);
+      return sl;
+    };
 
-      auto read_back_oldest = [&]() {
-        mbar_wait_bounded(done + 8 * rb, rbphase, p.status, dead);
-        tc_fence_after();
-        const float scale = pend[0];
-        const uint32_t d_tmem = d_base + rb * NT;
-        if (HN == 8) {
-          float d[8];
-          tc_ld8(d_tmem, d);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = fmaf(scale, d[i], acc[i]);
-        } else {
-#pragma unroll
-          for (int m0 = 0; m0 < HN; m0 += 16) {
-            float d[16];
-            tc_ld16(d_tmem + m0, d);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[(m0 + i) % HN] = fmaf(scale, d[i], acc[(m0 + i) % HN]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i + 1 < DEFER; ++i) pend[i] = pend[i + 1];
-        if (++rb == R) { rb = 0; rbphase ^= 1; }
-        --npend;
-      };
-
-      while (unit < unit1) {
-        const int cnt = ((unit & 1) == 0 && unit + 1 < unit1) ? 2 : 1;
-        // 1.0 unless the strip has group scales; converted only when queued, so the load's latency is hidden
-        unsigned short scale_raw = 0x3C00;
-        if (group && col_live) scale_raw = __ldg(sp);
-        sp += scale_stride;
-        mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
-        const bool mine = team < cnt;                 // this team's unit exists in the segment
-        if (mine) {
-          const uint8_t* st = smem + stage * kStageW;
-          uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, two = lo;
-          if (col_live) {
-            lo = *reinterpret_cast<const uint4*>(st + my_off);          // words 0..3
-            hi = *reinterpret_cast<const uint4*>(st + (my_off ^ 16));   // words 4..7
-            if (is6) two = *reinterpret_cast<const uint4*>(st + two_off);
-          }
-          // The operand slot and the accumulator tile of ring entry r were last used R segments ago;
-          // that segment was read back (after a wait on its `done`) before this point in program order.
-          const uint32_t a_tmem = a_base + r * 64;
-          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-          const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
-#pragma unroll
-          for (int step = 0; step < 4; ++step) {
-            uint32_t regs[8];
-            if (is6) {
-              expand_fp6(words[2 * step], twos[step], 0, regs);
-              expand_fp6(words[2 * step + 1], twos[step], 4, regs + 4);
-            } else {
-              expand_int4(words[2 * step], regs);
-              expand_int4(words[2 * step + 1], regs + 4);
-            }
-            tc_st8(a_tmem + step * 8, regs);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
-        tc_wait_st();
-        tc_fence_before();
-        if (lane == 0) mbar_arrive(ready + 8 * r);
-        if (npend == DEFER) read_back_oldest();       // segment n - DEFER: its MMAs finished long ago
-        {
-          const float sc = __half2float(__ushort_as_half(scale_raw));
-#pragma unroll
-          for (int i = 0; i < DEFER; ++i)
-            if (npend == i) pend[i] = sc;
-        }
-        ++npend;
-        unit += cnt;
-        if (++stage == S) { stage = 0; wphase ^= 1; }
-        if (++r == R) r = 0;
-      }
-      while (npend > 0) read_back_oldest();
-      u = slice_u1;
-
-      // ---------------- the strip is finished for this CTA: write C, or publish a partial
-      const bool full_strip = slice_u0 == s_begin && slice_u1 == s_end;
-      const int ncols = strip_cols(is6 ? geo.n6 : geo.n4, strip);
-      const int gcol = (is6 ? geo.n4 : 0) + strip * kStripCols + c;
+    // ---------------- the strip is finished for this CTA: write C, or publish a partial
+    auto finish_slice = [&](const Slice& sl, float (&out)[HN]) {
+      const int s_begin = sl.s_begin, s_end = s_begin + ups;
+      const bool full_strip = sl.u0 == s_begin && sl.u1 == s_end;
+      const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
       const bool writes = c < ncols;
       float col_scale = 1.f;      // per-channel INT4: s; FP6: s * 4096; group INT4: already applied
-      if (writes && !group) {
-        const half* sp = p.S + (is6 ? fp6_scale_offset(geo, strip) : int4_scale_offset(geo, strip, 0));
-        col_scale = __half2float(__ldg(sp + c)) * (is6 ? 4096.f : 1.f);
+      if (writes && !sl.group) {
+        const half* sp = p.S + (sl.is6 ? fp6_scale_offset(geo, sl.strip) : int4_scale_offset(geo, sl.strip, 0));
+        col_scale = __half2float(__ldg(sp + c)) * (sl.is6 ? 4096.f : 1.f);
       }
-      const int row0 = team * HN;                    // this thread's rows of A and C
       if (full_strip) {
         if (writes) {
 #pragma unroll
           for (int m = 0; m < HN; ++m)
-            if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(acc[m] * col_scale);
+            if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(out[m] * col_scale);
         }
-      } else {
-        float* slot_base = p.partials + (size_t)(2 * cta + (strip_lin != strip_first ? 1 : 0)) * C::kSlotFloats;
-#pragma unroll
-        for (int m = 0; m < HN; ++m) __stcg(slot_base + (row0 + m) * kStripCols + c, acc[m]);
-        int c_lo = cta, c_hi = cta;
-        while (c_lo > 0 && p.sched.bound[c_lo] > s_begin) --c_lo;
-        while (c_hi + 1 < p.sched.ctas && p.sched.bound[c_hi + 1] < s_end) ++c_hi;
-        named_bar_sync(1, kDequantThreads);          // every thread's partial stores are issued
-        if (dtid == 0) {
-          int contributors = 0;
-          for (int cc = c_lo; cc <= c_hi; ++cc) contributors += p.sched.bound[cc] < p.sched.bound[cc + 1];
-          const int last = atomic_add_acq_rel(p.counters + strip_lin, 1) == contributors - 1;
-          if (last) p.counters[strip_lin] = 0;       // the workspace is left zeroed, as the reference leaves its locks
-          misc[1] = last;
-        }
-        named_bar_sync(1, kDequantThreads);
-        if (misc[1] != 0) {
-          // the last CTA to arrive sums the slots in CTA order (deterministic) and writes C
-          float sum[HN];
-#pragma unroll
-          for (int m = 0; m < HN; ++m) sum[m] = 0.f;
-          constexpr int kBatch = HN <= 8 ? 4 : (HN <= 16 ? 2 : 1);   // slots whose loads are in flight together
-          for (int cbase = c_lo; cbase <= c_hi; cbase += kBatch) {
-            float v[kBatch][HN];
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i) {
-              const int cc = cbase + i;
-              const bool live = cc <= c_hi && p.sched.bound[cc] < p.sched.bound[cc + 1];
-              const int cc_first = live ? p.sched.bound[cc] / ups : 0;
-              const float* src = p.partials + (size_t)(2 * (live ? cc : cta) + (live && strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + row0 * kStripCols + c;
-#pragma unroll
-              for (int m = 0; m < HN; ++m) v[i][m] = live ? __ldcg(src + m * kStripCols) : 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i)
-#pragma unroll
-              for (int m = 0; m < HN; ++m) sum[m] += v[i][m];
-          }
-          if (writes) {
-#pragma unroll
-            for (int m = 0; m < HN; ++m)
-              if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
-          }
-        }
-        named_bar_sync(1, kDequantThreads);          // the flag may be rewritten by the next strip
+        return;
       }
+      float* slot_base = p.partials + (size_t)(2 * cta + (sl.strip_lin != strip_first ? 1 : 0)) * C::kSlotFloats;
+#pragma unroll
+      for (int m = 0; m < HN; ++m) __stcg(slot_base + (row0 + m) * kStripCols + c, out[m]);
+      int c_lo = cta, c_hi = cta;
+      while (c_lo > 0 && p.sched.bound[c_lo] > s_begin) --c_lo;
+      while (c_hi + 1 < p.sched.ctas && p.sched.bound[c_hi + 1] < s_end) ++c_hi;
+      named_bar_sync(1, kDequantThreads);          // every thread's partial stores are issued
+      if (dtid == 0) {
+        int contributors = 0;
+        for (int cc = c_lo; cc <= c_hi; ++cc) contributors += p.sched.bound[cc] < p.sched.bound[cc + 1];
+        const int last = atomic_add_acq_rel(p.counters + sl.strip_lin, 1) == contributors - 1;
+        if (last) p.counters[sl.strip_lin] = 0;    // the workspace is left zeroed, as the reference leaves its locks
+        misc[1] = last;
+      }
+      named_bar_sync(1, kDequantThreads);
+      if (misc[1] != 0) {
+        // the last CTA to arrive sums the slots in CTA order (deterministic) and writes C
+        float sum[HN];
+#pragma unroll
+        for (int m = 0; m < HN; ++m) sum[m] = 0.f;
+        constexpr int kBatch = HN <= 8 ? 4 : (HN <= 16 ? 2 : 1);   // slots whose loads are in flight together
+        for (int cbase = c_lo; cbase <= c_hi; cbase += kBatch) {
+          float v[kBatch][HN];
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i) {
+            const int cc = cbase + i;
+            const bool live = cc <= c_hi && p.sched.bound[cc] < p.sched.bound[cc + 1];
+            const int cc_first = live ? p.sched.bound[cc] / ups : 0;
+            const float* src = p.partials + (size_t)(2 * (live ? cc : cta) + (live && sl.strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + row0 * kStripCols + c;
+#pragma unroll
+            for (int m = 0; m < HN; ++m) v[i][m] = live ? __ldcg(src + m * kStripCols) : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+            for (int m = 0; m < HN; ++m) sum[m] += v[i][m];
+        }
+        if (writes) {
+#pragma unroll
+          for (int m = 0; m < HN; ++m)
+            if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
+        }
+      }
+      named_bar_sync(1, kDequantThreads);          // the flag may be rewritten by the next strip
+    };
+
+    // expands one unit (eight words of this thread's column, plus the two-bit part for FP6) into the
+    // operand slot at a_tmem (32 TMEM columns)
+    auto expand_unit = [&](bool is6, const uint4& lo, const uint4& hi, const uint4& two, uint32_t a_tmem) {
+      const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+      const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
+#pragma unroll
+      for (int step = 0; step < 4; ++step) {
+        uint32_t regs[8];
+        if (is6) {
+          expand_fp6(words[2 * step], twos[step], 0, regs);
+          expand_fp6(words[2 * step + 1], twos[step], 4, regs + 4);
+        } else {
+          expand_int4(words[2 * step], regs);
+          expand_int4(words[2 * step + 1], regs + 4);
+        }
+        tc_st8(a_tmem + step * 8, regs);
+      }
+    };
+
+    if constexpr (!C::kAlt) {
+      // ---------------------------------------------------------------- both teams on every segment
+      // Team t expands unit t of the segment and reads back rows [t NT/2, (t+1) NT/2) of its
+      // accumulator tile R - 1 segments later.
+      constexpr int DEFER = R - 1;
+      const uint32_t d_base = lane_base + C::kTmemD + team * HN;     // + r * NT
+      const uint32_t a_base = lane_base + C::kTmemA + team * 32;     // + r * 64
+      float acc[HN];
 #pragma unroll
       for (int m = 0; m < HN; ++m) acc[m] = 0.f;
-      ++strip_lin;
+      int stage = 0, r = 0, rb = 0;                  // weights stage, ring entry to fill, ring entry to read back
+      uint32_t wphase = 0, rbphase = 0;
+      int strip_lin = strip_first;
+      int u = U0;
+      while (u < U1) {
+        const Slice sl = open_slice(strip_lin, u);
+        const bool is6 = sl.is6;
+        const bool col_live = c < sl.nq * kQuadCols;     // padded quads of a ragged strip hold no data
+        const uint32_t unit_bytes = sl.nq * (is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
+        int unit = u - sl.s_begin;
+        const int unit1 = sl.u1 - sl.s_begin;
+        const uint32_t my_off = team * unit_bytes + lds_lo;
+        const uint32_t two_off = team * unit_bytes + sl.nq * kInt4UnitQuadBytes + c * 16;
+        const int scale_stride = sl.nq * kQuadCols;
+        const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.S) +
+                                   (sl.group ? int4_scale_offset(geo, sl.strip, 0) + c + (size_t)(unit >> 1) * scale_stride : 0);
+        int npend = 0;                                   // segments whose accumulator tile is not read back yet
+        float pend[DEFER];                               // their group scales, oldest first
+#pragma unroll
+        for (int i = 0; i < DEFER; ++i) pend[i] = 1.f;
+
+        auto read_back_oldest = [&]() {
+          mbar_wait_bounded(done + 8 * rb, rbphase, p.status, dead);
+          tc_fence_after();
+          const float scale = pend[0];
+          const uint32_t d_tmem = d_base + rb * NT;
+          if (HN == 8) {
+            float d[8];
+            tc_ld8(d_tmem, d);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(scale, d[i], acc[i]);
+          } else {
+#pragma unroll
+            for (int m0 = 0; m0 < HN; m0 += 16) {
+              float d[16];
+              tc_ld16(d_tmem + m0, d);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[(m0 + i) % HN] = fmaf(scale, d[i], acc[(m0 + i) % HN]);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i + 1 < DEFER; ++i) pend[i] = pend[i + 1];
+          if (++rb == R) { rb = 0; rbphase ^= 1; }
+          --npend;
+        };
+
+        while (unit < unit1) {
+          const int cnt = ((unit & 1) == 0 && unit + 1 < unit1) ? 2 : 1;
+          // 1.0 unless the strip has group scales; converted only when queued, so the load's latency is hidden
+          unsigned short scale_raw = 0x3C00;
+          if (sl.group && col_live) scale_raw = __ldg(sp);
+          sp += scale_stride;
+          mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
+          if (team < cnt) {                              // this team's unit exists in the segment
+            // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
+            const uint8_t* st = smem + stage * kStageW;
+            const uint4 lo = *reinterpret_cast<const uint4*>(st + my_off);          // words 0..3
+            const uint4 hi = *reinterpret_cast<const uint4*>(st + (my_off ^ 16));   // words 4..7
+            uint4 two = make_uint4(0, 0, 0, 0);
+            if (is6) two = *reinterpret_cast<const uint4*>(st + two_off);
+            // The operand slot and the accumulator tile of ring entry r were last used R segments ago;
+            // that segment was read back (after a wait on its `done`) before this point in program order.
+            expand_unit(is6, lo, hi, two, a_base + r * 64);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
+          tc_wait_st();
+          tc_fence_before();
+          if (lane == 0) mbar_arrive(ready + 8 * r);
+          if (npend == DEFER) read_back_oldest();       // segment n - DEFER: its MMAs finished long ago
+          {
+            const float sc = __half2float(__ushort_as_half(scale_raw));
+#pragma unroll
+            for (int i = 0; i < DEFER; ++i)
+              if (npend == i) pend[i] = sc;
+          }
+          ++npend;
+          unit += cnt;
+          if (++stage == S) { stage = 0; wphase ^= 1; }
+          if (++r == R) r = 0;
+        }
+        while (npend > 0) read_back_oldest();
+        u = sl.u1;
+        finish_slice(sl, acc);
+#pragma unroll
+        for (int m = 0; m < HN; ++m) acc[m] = 0.f;
+        ++strip_lin;
+      }
+    } else {
+      // ---------------------------------------------------------------- the teams take alternate segments
+      // Team t owns the segments with global index n = t, t + 2, ...: it expands both units, and after
+      // storing segment n it reads back all NT rows of segment n - 2.  Two independent chains per CTA
+      // hide each other's latencies; the partial sums of the teams are swapped through shared memory
+      // at the end of a slice so that each thread finishes with its own half of the rows.
+      const uint32_t d_base = lane_base + C::kTmemD;       // + r * NT
+      const uint32_t a_base = lane_base + C::kTmemA;       // + r * 64
+      float acc[NT];
+#pragma unroll
+      for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+      int n = team;                                  // global index of this team's next segment
+      int stage = team, r = team;                    // n % S, n % R
+      uint32_t wphase = 0, rphase = 0;               // (n / S) & 1, (n / R) & 1
+      int n0 = 0;                                    // global index of the slice's first segment
+      int strip_lin = strip_first;
+      int u = U0;
+      while (u < U1) {
+        const Slice sl = open_slice(strip_lin, u);
+        const bool is6 = sl.is6;
+        const bool col_live = c < sl.nq * kQuadCols;     // padded quads of a ragged strip hold no data
+        const uint32_t unit_bytes = sl.nq * (is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
+        const int unit0 = u - sl.s_begin, unit1 = sl.u1 - sl.s_begin;
+        const int b0 = unit0 >> 1;                        // first 128-row block of the slice
+        const int nseg = ((unit1 + 1) >> 1) - b0;         // one segment per block that the slice touches
+        const uint32_t two_off = sl.nq * kInt4UnitQuadBytes + c * 16;
+        const int scale_stride = sl.nq * kQuadCols;
+        const unsigned short* sp0 = reinterpret_cast<const unsigned short*>(p.S) +
+                                    (sl.group ? int4_scale_offset(geo, sl.strip, 0) + c : 0);
+        bool pending = false;                            // a segment of this team is not read back yet
+        int pr = 0;
+        uint32_t prphase = 0;
+        float pscale = 1.f;
+
+        auto read_back = [&]() {
+          mbar_wait_bounded(done + 8 * pr, prphase, p.status, dead);
+          tc_fence_after();
+          const uint32_t d_tmem = d_base + pr * NT;
+#pragma unroll
+          for (int m0 = 0; m0 < NT; m0 += 16) {
+            float d[16];
+            tc_ld16(d_tmem + m0, d);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[m0 + i] = fmaf(pscale, d[i], acc[m0 + i]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(d_free + 8 * pr);    // the MMA issuer may overwrite the tile
+          pending = false;
+        };
+
+        for (int j = n - n0; j < nseg; j += 2) {
+          const int b = b0 + j;
+          const int cnt = min(unit1, 2 * b + 2) - max(unit0, 2 * b);
+          // 1.0 unless the strip has group scales; converted only when queued, so the load's latency is hidden
+          unsigned short scale_raw = 0x3C00;
+          if (sl.group && col_live) scale_raw = __ldg(sp0 + (size_t)b * scale_stride);
+          mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
+          // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
+          const uint8_t* st = smem + stage * kStageW;
+          const uint4 lo0 = *reinterpret_cast<const uint4*>(st + lds_lo);          // words 0..3
+          const uint4 hi0 = *reinterpret_cast<const uint4*>(st + (lds_lo ^ 16));   // words 4..7
+          uint4 two0 = make_uint4(0, 0, 0, 0);
+          if (is6) two0 = *reinterpret_cast<const uint4*>(st + two_off);
+          // the MMAs that read this ring entry's operand slot R segments ago have finished
+          mbar_wait_bounded(done + 8 * r, rphase ^ 1, p.status, dead);
+          tc_fence_after();
+          const uint32_t a_tmem = a_base + r * 64;
+          expand_unit(is6, lo0, hi0, two0, a_tmem);
+          if (cnt == 2) {
+            const uint8_t* st1 = st + unit_bytes;
+            const uint4 lo1 = *reinterpret_cast<const uint4*>(st1 + lds_lo);
+            const uint4 hi1 = *reinterpret_cast<const uint4*>(st1 + (lds_lo ^ 16));
+            uint4 two1 = make_uint4(0, 0, 0, 0);
+            if (is6) two1 = *reinterpret_cast<const uint4*>(st1 + two_off);
+            expand_unit(is6, lo1, hi1, two1, a_tmem + 32);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
+          tc_wait_st();
+          tc_fence_before();
+          if (lane == 0) mbar_arrive(ready + 8 * r);
+          if (pending) read_back();                      // this team's previous segment: its MMAs finished long ago
+          pending = true;
+          pr = r;
+          prphase = rphase;
+          pscale = __half2float(__ushort_as_half(scale_raw));
+          n += 2;
+          stage += 2;
+          if (stage >= S) { stage -= S; wphase ^= 1; }
+          r += 2;
+          if (r >= R) { r -= R; rphase ^= 1; }
+        }
+        if (pending) read_back();
+        n0 += nseg;
+        u = sl.u1;
+
+        // swap halves: rows this thread does not own go to the other team, its own rows come back
+        float out[HN];
+#pragma unroll
+        for (int i = 0; i < HN; ++i) xch[(team * HN + i) * kStripCols + c] = team ? acc[i] : acc[HN + i];
+        named_bar_sync(1, kDequantThreads);
+#pragma unroll
+        for (int i = 0; i < HN; ++i) out[i] = (team ? acc[HN + i] : acc[i]) + xch[((1 - team) * HN + i) * kStripCols + c];
+        named_bar_sync(1, kDequantThreads);              // the buffer may be rewritten by the next slice
+        finish_slice(sl, out);
+#pragma unroll
+        for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+        ++strip_lin;
+      }
     }
   }
 
@@ -510,9 +675,9 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   }
 }
 
-using Tc5Rows16 = Tc5Cfg<16, 7, 3, 2>;
-using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2>;
-using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2>;
+using Tc5Rows16 = Tc5Cfg<16, 7, 3, 2, true>;
+using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2, false>;
+using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2, false>;
 
 template <class C>
 cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
