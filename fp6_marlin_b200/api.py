@@ -197,7 +197,8 @@ def _device_buffers(device: torch.device):
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _scratch:
         nbytes = lib.fp6m_mul_scratch_bytes(0, 0, 0, 0, -1)
-        _scratch[idx] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        # zero once: the kernel keeps per-strip epoch words and tagged split-K slots in it between calls
+        _scratch[idx] = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
     return idx, _scratch[idx], _status[idx]
 

@@ -107,7 +107,8 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.S = static_cast<const half*>(s);
   p.N = N; p.K = K;
   p.counters = static_cast<int*>(workspace);
-  p.partials = static_cast<float*>(scratch);
+  p.epochs = static_cast<unsigned int*>(scratch);
+  p.partials = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(scratch) + kEpochWords * sizeof(unsigned int));
   p.status = status_dev;
 
   for (int m0 = 0; m0 < M; m0 += rows) {

@@ -74,15 +74,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Bounded wait.  `kSleepNs` > 0 is for roles that run far ahead of their consumers (producers): they
+// sleep between polls, so their polling does not take issue slots from the working warps.
+template <int kSleepNs = 0>
 __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, bool& dead) {
   // fast path: one potentially-blocking try_wait; in steady state the phase is complete already
   if (mbar_try_wait(bar, parity)) return;
   if (dead) return;
-  // try_wait parks the thread in hardware until the phase completes or the hint elapses, so waiting
-  // roles put no polling traffic on the shared-memory pipeline that the working warps also use
 #pragma unroll 1
-  for (int i = 0; i < (1 << 16); ++i)
-    if (mbar_try_wait_hint(bar, parity, 16384u)) return;     // up to 65536 x 16 us
+  for (int i = 0; i < (1 << 16); ++i) {                      // up to 65536 x (16 us + sleep)
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
+    if (mbar_try_wait_hint(bar, parity, 16384u)) return;
+  }
   dead = true;
   if (status) atomicExch(status, kStatusTimeout);
 }

@@ -17,11 +17,14 @@ struct MulParams {
   const half* S;        // scales, b200 order
   int M, N, K;
   Geometry geo;
-  int* counters;        // one zero-initialised int per strip (the caller's workspace)
-  float* partials;      // fp32 split-K slots (scratch)
+  int* counters;        // one zero-initialised int per strip (the caller's workspace; left untouched)
+  unsigned int* epochs;            // scratch header: [0] launch epoch, [1] CTAs of this launch that have read it
+  unsigned long long* partials;    // split-K slots (scratch): {fp32 value, epoch tag} per 64-bit word
   int* status;          // optional device status word
   Schedule sched;
 };
+
+constexpr int kEpochWords = 64;     // scratch header size in 32-bit words
 
 // gemm_tc5.cu
 int tc5_rows_per_pass();

@@ -55,7 +55,7 @@ struct Tc5Cfg {
   static constexpr int kCtasPerSm = CTAS_PER_SM_;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves
   static constexpr int kActBytes = 2 * kActUnitBytes;
-  static constexpr int kNumBars = 2 * kStages + (ALT_ ? 4 : 3) * kRing;
+  static constexpr int kNumBars = 2 * kStages + (ALT_ ? 4 : 3) * kRing + 1;
   static constexpr int kXchBytes = ALT_ ? NT * 128 * 4 : 0;   // the teams exchange half of their rows at the end of a slice
   static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kXchBytes + kNumBars * 8 + 64;
   static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
@@ -136,11 +136,49 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const unsigned int* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u32(unsigned int* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t atomic_add_relaxed_u32(unsigned int* addr, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.relaxed.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+  return old;
+}
 __device__ __forceinline__ int atomic_add_acq_rel(int* addr, int v) {
   int old;
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
   return old;
 }
+
+// Launch epoch.  Every CTA of a launch reads the epoch word and then counts itself; the CTA that
+// completes the count knows that all have read it and advances it for the next launch (also for
+// the next replay of a captured graph).  The counting atomic takes its address through the loaded
+// value, so it cannot be performed before the load.
+__device__ __forceinline__ uint32_t read_epoch_and_count(unsigned int* words, uint32_t ctas) {
+  const uint32_t e = ld_relaxed_u32(words);
+  uint32_t zero;
+  asm volatile("and.b32 %0, %1, 0;" : "=r"(zero) : "r"(e));
+  const uint32_t arrived = atomic_add_relaxed_u32(words + 1 + zero, 1u);
+  if (arrived == ctas - 1) {
+    st_relaxed_u32(words + 1, 0u);
+    st_relaxed_u32(words, e + 1);
+  }
+  return e;
+}
+
 
 // INT4 word -> the exact integers q - 8 as fp16 pairs (rows i0,i1 | i2,i3 | i4,i5 | i6,i7): the nibble is
 // OR-ed into the mantissa of 1024 (bits 0-3) or of 64 (bits 4-7) and the constant is subtracted.
@@ -203,13 +241,17 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   const uint32_t w_full = smem_u32(bars), w_empty = w_full + 8 * S;
   const uint32_t act_full = w_empty + 8 * S, ready = act_full + 8 * R, done = ready + 8 * R;
   const uint32_t d_free = done + 8 * R;    // ALT only: the accumulator tile has been read back
+  const uint32_t epoch_bar = smem_u32(bars + C::kNumBars - 1);   // misc[1] holds the launch epoch
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x;
   const Geometry& geo = p.geo;
   const int ups = units_per_strip(geo);
   const int U0 = p.sched.bound[cta], U1 = p.sched.bound[cta + 1];
-  if (U0 >= U1) return;
+  if (U0 >= U1) {                      // no work: still counted, see read_epoch_and_count
+    if (tid == 0) read_epoch_and_count(p.epochs, gridDim.x);
+    return;
+  }
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -222,6 +264,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       if (C::kAlt) mbar_init(d_free + 8 * r, 4);     // the team that owns the segment has read the accumulator tile back
       mbar_init(done + 8 * r, 1);        // tcgen05.commit: every MMA of the segment has finished
     }
+    mbar_init(epoch_bar, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -233,6 +276,13 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   tc_fence_after();
   const uint32_t tmem = misc[0];
   bool dead = false;
+
+  if (warp == 3 && lane == 0) {
+    // the tag of this launch's split-K partials is epoch + 1
+    const uint32_t e = read_epoch_and_count(p.epochs, gridDim.x);
+    misc[1] = e;
+    mbar_arrive(epoch_bar);
+  }
 
   if (warp == 0) {
     // ================================================================== weights producer
@@ -258,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
           }
         }
         const int cnt = it.count();
-        mbar_wait_bounded(empty, phase ^ 1, p.status, dead);
+        mbar_wait_bounded<200>(empty, phase ^ 1, p.status, dead);
         const uint32_t bytes = cnt * unit_bytes;            // consecutive units are contiguous in HBM
         mbar_arrive_expect_tx(full, bytes);
         tma_load_1d_stream(dst, wsrc, bytes, full, policy);
@@ -283,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
     uint32_t rphase = 0;
     while (it.valid()) {
       const int cnt = it.count();
-      mbar_wait_bounded(done + 8 * r, rphase ^ 1, p.status, dead);     // the MMAs that read this tile are done
+      mbar_wait_bounded<200>(done + 8 * r, rphase ^ 1, p.status, dead);     // the MMAs that read this tile are done
       const uint32_t dst = a_dst0 + r * C::kActBytes;
       for (int h = 0; h < cnt; ++h) {
         const int k0 = (it.unit + h) * kUnitRows;
@@ -319,9 +369,9 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       while (it.valid()) {
         const int cnt = it.count();
         if (kIssuers == 1 || (n & 1) == mine) {
-          mbar_wait_bounded(act_full + 8 * r, rphase, p.status, dead);
+          mbar_wait_bounded<40>(act_full + 8 * r, rphase, p.status, dead);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
-          mbar_wait_bounded(ready + 8 * r, rphase, p.status, dead);
+          mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
           if (C::kAlt) mbar_wait_bounded(d_free + 8 * r, rphase ^ 1, p.status, dead);   // previous tile of this entry was read
           tc_fence_after();
           const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
@@ -371,19 +421,39 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       return sl;
     };
 
-    // ---------------- the strip is finished for this CTA: write C, or publish a partial
-    auto finish_slice = [&](const Slice& sl, float (&out)[HN]) {
-      const int s_begin = sl.s_begin, s_end = s_begin + ups;
-      const bool full_strip = sl.u0 == s_begin && sl.u1 == s_end;
-      const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
-      const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
-      const bool writes = c < ncols;
+    // ---------------- the strip is finished for this CTA: write C, or store a partial sum
+    // Split-K without atomics or fences: a partial is stored as 64-bit words {fp32 value, tag}, the
+    // tag being the strip's epoch + 1 (the epoch word lives in the scratch header and is advanced by
+    // the strip's reducer, so every launch - also a replay of a captured graph - uses fresh tags).
+    // The reducer of a strip is its LAST contributor in CTA order, i.e. the CTA whose slice reaches
+    // the end of the strip; that slice is the first one of the CTA, and the reduction is postponed to
+    // the CTA's end (finish_cta), when the other contributors have normally finished.  It then
+    // reads the slots of the lower-numbered contributors, spinning (bounded) on words whose tag has
+    // not arrived, sums in CTA order (deterministic) and writes C.  Only lower-numbered CTAs are
+    // waited for, and those were dispatched earlier.  Only the first and the last slice of a CTA can
+    // be partial; the caller's workspace is not touched.
+    int reduce_strip = -1;                           // strip this CTA must reduce at its end
+    uint32_t reduce_tag = 0;
+    auto column_scale = [&](const Slice& sl, bool writes) {
       float col_scale = 1.f;      // per-channel INT4: s; FP6: s * 4096; group INT4: already applied
       if (writes && !sl.group) {
         const half* sp = p.S + (sl.is6 ? fp6_scale_offset(geo, sl.strip) : int4_scale_offset(geo, sl.strip, 0));
         col_scale = __half2float(__ldg(sp + c)) * (sl.is6 ? 4096.f : 1.f);
       }
-      if (full_strip) {
+      return col_scale;
+    };
+    auto slot_of = [&](int cc, int strip_lin) {
+      // slot 0 holds the partial of a CTA's first strip, slot 1 that of its last strip
+      const int cc_first = p.sched.bound[cc] / ups;
+      return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + row0 * kStripCols + c;
+    };
+    auto finish_slice = [&](const Slice& sl, float (&out)[HN]) {
+      const int s_begin = sl.s_begin, s_end = s_begin + ups;
+      if (sl.u0 == s_begin && sl.u1 == s_end) {      // the whole strip was ours
+        const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+        const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
+        const bool writes = c < ncols;
+        const float col_scale = column_scale(sl, writes);
         if (writes) {
 #pragma unroll
           for (int m = 0; m < HN; ++m)
@@ -391,50 +461,75 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         }
         return;
       }
-      float* slot_base = p.partials + (size_t)(2 * cta + (sl.strip_lin != strip_first ? 1 : 0)) * C::kSlotFloats;
+      mbar_wait_bounded(epoch_bar, 0, p.status, dead);   // completed long ago: orders the read of misc[1]
+      const uint32_t tag = misc[1] + 1;
+      unsigned long long* slot = slot_of(cta, sl.strip_lin);
 #pragma unroll
-      for (int m = 0; m < HN; ++m) __stcg(slot_base + (row0 + m) * kStripCols + c, out[m]);
-      int c_lo = cta, c_hi = cta;
-      while (c_lo > 0 && p.sched.bound[c_lo] > s_begin) --c_lo;
-      while (c_hi + 1 < p.sched.ctas && p.sched.bound[c_hi + 1] < s_end) ++c_hi;
-      named_bar_sync(1, kDequantThreads);          // every thread's partial stores are issued
-      if (dtid == 0) {
-        int contributors = 0;
-        for (int cc = c_lo; cc <= c_hi; ++cc) contributors += p.sched.bound[cc] < p.sched.bound[cc + 1];
-        const int last = atomic_add_acq_rel(p.counters + sl.strip_lin, 1) == contributors - 1;
-        if (last) p.counters[sl.strip_lin] = 0;    // the workspace is left zeroed, as the reference leaves its locks
-        misc[1] = last;
+      for (int m = 0; m < HN; ++m)
+        st_relaxed_u64(slot + m * kStripCols, ((unsigned long long)tag << 32) | __float_as_uint(out[m]));
+      if (sl.u1 == s_end) {                          // last contributor of the strip: reduce it at the end
+        reduce_strip = sl.strip_lin;
+        reduce_tag = tag;
       }
-      named_bar_sync(1, kDequantThreads);
-      if (misc[1] != 0) {
-        // the last CTA to arrive sums the slots in CTA order (deterministic) and writes C
-        float sum[HN];
+    };
+
+    // ---------------- after the last slice: reduce the strip whose last contributor this CTA is
+    auto finish_cta = [&]() {
+      if (reduce_strip < 0) return;
+      const Slice sl = open_slice(reduce_strip, 0);
+      int c_lo = cta;
+      while (c_lo > 0 && p.sched.bound[c_lo] > sl.s_begin) --c_lo;
+      float sum[HN];
 #pragma unroll
-        for (int m = 0; m < HN; ++m) sum[m] = 0.f;
-        constexpr int kBatch = HN <= 8 ? 4 : (HN <= 16 ? 2 : 1);   // slots whose loads are in flight together
-        for (int cbase = c_lo; cbase <= c_hi; cbase += kBatch) {
-          float v[kBatch][HN];
+      for (int m = 0; m < HN; ++m) sum[m] = 0.f;
+      // 16 tagged words are in flight together: kBatch contributors x kRows rows
+      constexpr int kRows = HN < 16 ? HN : 16;
+      constexpr int kBatch = 16 / kRows;
+      for (int cbase = c_lo; cbase <= cta; cbase += kBatch) {
+        bool live[kBatch];
+        const unsigned long long* src[kBatch];
 #pragma unroll
-          for (int i = 0; i < kBatch; ++i) {
-            const int cc = cbase + i;
-            const bool live = cc <= c_hi && p.sched.bound[cc] < p.sched.bound[cc + 1];
-            const int cc_first = live ? p.sched.bound[cc] / ups : 0;
-            const float* src = p.partials + (size_t)(2 * (live ? cc : cta) + (live && sl.strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + row0 * kStripCols + c;
+        for (int i = 0; i < kBatch; ++i) {
+          const int cc = cbase + i;
+          live[i] = cc <= cta && p.sched.bound[cc] < p.sched.bound[cc + 1];
+          src[i] = slot_of(live[i] ? cc : cta, reduce_strip);
+        }
 #pragma unroll
-            for (int m = 0; m < HN; ++m) v[i][m] = live ? __ldcg(src + m * kStripCols) : 0.f;
+        for (int m0 = 0; m0 < HN; m0 += kRows) {
+          unsigned long long v[kBatch][kRows];
+          bool all_here = false;
+#pragma unroll 1
+          for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+              for (int m = 0; m < kRows; ++m) v[i][m] = ld_relaxed_u64(src[i] + (m0 + m) * kStripCols);
+            all_here = true;
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+              for (int m = 0; m < kRows; ++m) all_here = all_here && (!live[i] || (uint32_t)(v[i][m] >> 32) == reduce_tag);
+            if (dead) break;
+          }
+          if (!all_here && !dead) {
+            dead = true;
+            if (p.status) atomicExch(p.status, kStatusTimeout);
           }
 #pragma unroll
           for (int i = 0; i < kBatch; ++i)
 #pragma unroll
-            for (int m = 0; m < HN; ++m) sum[m] += v[i][m];
-        }
-        if (writes) {
-#pragma unroll
-          for (int m = 0; m < HN; ++m)
-            if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
+            for (int m = 0; m < kRows; ++m) sum[m0 + m] += live[i] ? __uint_as_float((uint32_t)v[i][m]) : 0.f;
         }
       }
-      named_bar_sync(1, kDequantThreads);          // the flag may be rewritten by the next strip
+      const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
+      const bool writes = c < ncols;
+      const float col_scale = column_scale(sl, writes);
+      if (writes) {
+#pragma unroll
+        for (int m = 0; m < HN; ++m)
+          if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
+      }
     };
 
     // expands one unit (eight words of this thread's column, plus the two-bit part for FP6) into the
@@ -554,6 +649,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         for (int m = 0; m < HN; ++m) acc[m] = 0.f;
         ++strip_lin;
       }
+      finish_cta();
     } else {
       // ---------------------------------------------------------------- the teams take alternate segments
       // Team t owns the segments with global index n = t, t + 2, ...: it expands both units, and after
@@ -664,6 +760,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         for (int m = 0; m < NT; ++m) acc[m] = 0.f;
         ++strip_lin;
       }
+      finish_cta();
     }
   }
 
@@ -702,7 +799,7 @@ int tc5_ctas_per_sm(int rows) { return rows <= 16 ? Tc5Rows16::kCtasPerSm : (row
 
 size_t tc5_scratch_bytes(int ctas, int rows) {
   const int nt = rows <= 16 ? 16 : (rows <= 32 ? 32 : 64);
-  return (size_t)2 * ctas * nt * kStripCols * sizeof(float);
+  return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * nt * kStripCols * sizeof(unsigned long long);
 }
 
 // Runs the GEMM for rows [0, p.M) with p.M <= 64; the host dispatcher loops over larger M.

@@ -87,7 +87,9 @@ int fp6m_schedule(int K, int N, int qc, int group_size, int ctas, int* bounds);
 /* GPU side: the GEMM                                                                         */
 /* ------------------------------------------------------------------------------------------ */
 
-/* Bytes of scratch (device memory, any contents) fp6m_mul needs for this shape; 256-byte aligned. */
+/* Bytes of scratch (device memory) fp6m_mul needs for this shape; 256-byte aligned.  The buffer must be
+ * all zero the first time it is used and is otherwise private to fp6m_mul: keep passing it as it was left
+ * (it holds per-strip epoch words and tagged split-K slots), or pass a freshly zeroed one. */
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms);
 
 /* C[M,N] (fp16, row-major, overwritten) = A[M,K] (fp16, row-major) x dequant(B, s).
@@ -96,8 +98,9 @@ size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms);
  * arguments (thread_k, thread_n, sms, max_par are validated exactly as the reference validates
  * them and otherwise treated as hints), same return codes 0/1/2, asynchronous on `stream`.
  *   workspace       >= N/128*max_par 32-bit words, all zero on entry, left all zero on exit
- *                   (the reference's lock array; here it holds the per-strip arrival counters)
- *   scratch         >= fp6m_mul_scratch_bytes(...) bytes of device memory for fp32 split-K partials
+ *                   (the reference's lock array; validated like the reference does, not written)
+ *   scratch         >= fp6m_mul_scratch_bytes(...) bytes of device memory for the split-K partials,
+ *                   zeroed before its first use (see fp6m_mul_scratch_bytes)
  *   quant_cols      number of FP6 columns (last columns of B); -1 = none
  *   group_size      128 or -1 (per-channel)
  *   layout          FP6M_LAYOUT_B200 (FP6M_LAYOUT_REFERENCE is converted by
@@ -113,16 +116,16 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
  * inside a host runtime that owns the whole memory arena, code running after an allocator freeze
  * or while other threads hold the device in a state where cudaMalloc's implicit synchronisation is
  * not acceptable.  The split-K scratch is a static array inside the library (FP6M_STATIC_SCRATCH_BYTES,
- * 8 MiB, resident on every GPU that loads the library until the process exits); the caller still
+ * 16 MiB, resident on every GPU that loads the library until the process exits); the caller still
  * passes A, B, C, s and the workspace.  This entry point has no counterpart in the reference.
  *   - Enough for up to 16 rows of A per call on any grid (larger M fits when `sms` limits the grid);
  *     a call that would need more returns FP6M_ERR_SCRATCH and launches nothing.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress); make
  *     that first call outside any stream capture.
  *   - All calls share the one array: calls that can overlap on the GPU (different streams) race.
- *     Nothing in it has to be zero between calls.
+ *     It starts out zeroed and needs no attention between calls.
  *   - Never calls cudaMalloc, cudaFree or any allocating routine. */
-#define FP6M_STATIC_SCRATCH_BYTES (8u << 20)
+#define FP6M_STATIC_SCRATCH_BYTES (16u << 20)
 int fp6m_mul_static_scratch(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
                             void* workspace, size_t workspace_bytes, int dev, void* stream,
                             int thread_k, int thread_n, int sms, int max_par,
