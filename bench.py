@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sweep", action="store_true", help="also time the other M values and layer shapes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="launch the GEMMs without programmatic dependent launch (no overlap of consecutive steps)")
     return ap.parse_args()
 
 
@@ -246,6 +248,9 @@ def b200_arm(args):
     c_host = torch.zeros((world, M_ROWS, n_local), dtype=torch.float16).pin_memory()
     workspace = torch.zeros(max(n_local // 128 * 16, 64), dtype=torch.int32, device=dev)
     stream = torch.cuda.Stream(device=dev)
+    # consecutive GEMMs of a decode step: each may set itself up and prefetch its (static) weights while
+    # the previous kernel of the stream drains; activations, outputs and scratch wait for that kernel
+    fm.set_launch_overlap(not args.no_overlap)
 
     def step(i, a):
         B, s = copies[i % n_copies]
@@ -329,7 +334,7 @@ def b200_arm(args):
                    "quant_cols": QUANT_COLS, "group_size": GROUP,
                    "l2": f"{n_copies} rotating weight copies ({n_copies * weight.B.numel() * 4 / 1e6:.0f} MB) exceed L2",
                    "parallelism": "single GPU" if world == 1 else f"N-sharded over {world} GPUs + NCCL all-gather of output columns",
-                   "graph": True},
+                   "graph": True, "launch_overlap": not args.no_overlap},
         "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": M_ROWS * N_DIM * 2},
         "gpu_launches": args.steps,

@@ -36,6 +36,7 @@ SIGNATURES = {
     "fp6m_mul_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _i, _vp,
                                      _i, _i, _i, _i, _i, _i, _i, _vp]),
     "fp6m_dump_operands": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "fp6m_set_launch_overlap": (ctypes.c_int, [ctypes.c_int]),
     "fp6m_last_cuda_error": (ctypes.c_char_p, []),
     "fp6m_version": (ctypes.c_char_p, []),
 }

@@ -203,6 +203,15 @@ def _device_buffers(device: torch.device):
     return idx, _scratch[idx], _status[idx]
 
 
+def set_launch_overlap(enable: bool) -> bool:
+    """Process-wide switch for programmatic dependent launch of the GEMM kernels (off by default);
+    returns the previous setting.  When on, a GEMM may set itself up and prefetch its weights while the
+    kernel before it in the stream is finishing; A, C and the scratch are only touched after that kernel
+    has completed.  Only turn it on when the kernel preceding a GEMM in its stream does not write that
+    GEMM's weights or scales."""
+    return bool(lib.fp6m_set_launch_overlap(1 if enable else 0))
+
+
 def device_status(device=None) -> int:
     """Reads (and clears) the device status word: 0, or FP6M_ERR_TIMEOUT (8) if a bounded wait
     inside a kernel ran out since the last call.  Synchronises the device."""

@@ -157,6 +157,12 @@ int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, 
   return e == cudaSuccess ? FP6M_OK : cuda_fail(e, "dump_operands launch");
 }
 
+int fp6m_set_launch_overlap(int enable) {
+  const int before = tc5_get_overlap() ? 1 : 0;
+  if (enable >= 0) tc5_set_overlap(enable != 0);
+  return before;
+}
+
 const char* fp6m_last_cuda_error(void) { return g_cuda_error; }
 
 const char* fp6m_version(void) { return "fp6m-b200 0.1 (sm_100a)"; }

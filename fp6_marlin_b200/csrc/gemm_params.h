@@ -30,6 +30,8 @@ constexpr int kEpochWords = 64;     // scratch header size in 32-bit words
 int tc5_rows_per_pass();
 int tc5_ctas_per_sm(int rows);
 size_t tc5_scratch_bytes(int ctas, int rows);
+void tc5_set_overlap(bool on);
+bool tc5_get_overlap();
 cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 
 // dump_operands.cu

@@ -65,6 +65,15 @@ struct Tc5Cfg {
   static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 };
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// launch_dependents: the next kernel of the stream may start launching (it runs its set-up and
+// prefetches weights while this one finishes).  grid_dependency_wait: returns once every kernel this
+// one depends on has completed and its writes are visible; without a programmatic dependency both
+// are no-ops.  Everything that earlier kernels may have written (A, C, the scratch) is only touched
+// after the wait; the weights and scales are read before it.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -248,8 +257,12 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   const Geometry& geo = p.geo;
   const int ups = units_per_strip(geo);
   const int U0 = p.sched.bound[cta], U1 = p.sched.bound[cta + 1];
+  launch_dependents();
   if (U0 >= U1) {                      // no work: still counted, see read_epoch_and_count
-    if (tid == 0) read_epoch_and_count(p.epochs, gridDim.x);
+    if (tid == 0) {
+      grid_dependency_wait();
+      read_epoch_and_count(p.epochs, gridDim.x);
+    }
     return;
   }
 
@@ -279,6 +292,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
 
   if (warp == 3 && lane == 0) {
     // the tag of this launch's split-K partials is epoch + 1
+    grid_dependency_wait();
     const uint32_t e = read_epoch_and_count(p.epochs, gridDim.x);
     misc[1] = e;
     mbar_arrive(epoch_bar);
@@ -331,6 +345,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
     it.init(U0, U1, ups);
     int r = 0;
     uint32_t rphase = 0;
+    grid_dependency_wait();                           // A may come from the previous kernel
     while (it.valid()) {
       const int cnt = it.count();
       mbar_wait_bounded<200>(done + 8 * r, rphase ^ 1, p.status, dead);     // the MMAs that read this tile are done
@@ -448,6 +463,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + row0 * kStripCols + c;
     };
     auto finish_slice = [&](const Slice& sl, float (&out)[HN]) {
+      grid_dependency_wait();                        // C and the scratch may still be in use by the previous kernel
       const int s_begin = sl.s_begin, s_end = s_begin + ups;
       if (sl.u0 == s_begin && sl.u1 == s_end) {      // the whole strip was ours
         const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
@@ -776,6 +792,8 @@ using Tc5Rows16 = Tc5Cfg<16, 7, 3, 2, true>;
 using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2, false>;
 using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2, false>;
 
+bool g_overlap_launches = false;
+
 template <class C>
 cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
   static bool configured[64] = {};
@@ -786,13 +804,25 @@ cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  w46_gemm_tc5_kernel<C><<<p.sched.ctas, kThreads, C::kSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.sched.ctas);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_overlap_launches ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w46_gemm_tc5_kernel<C>, p);
 }
 
 }  // namespace
 
 int tc5_rows_per_pass() { return 64; }
+
+void tc5_set_overlap(bool on) { g_overlap_launches = on; }
+bool tc5_get_overlap() { return g_overlap_launches; }
 
 // CTAs per SM the kernel is sized for, for `rows` rows of A in one pass.
 int tc5_ctas_per_sm(int rows) { return rows <= 16 ? Tc5Rows16::kCtasPerSm : (rows <= 32 ? Tc5Rows32::kCtasPerSm : Tc5Rows64::kCtasPerSm); }

@@ -138,6 +138,14 @@ int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, 
                        int group_size, int dev, void* stream);
 
 /* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
+/* Process-wide option, off by default; returns the previous setting (a negative argument only queries).
+ * When on, the GEMM kernels are launched with programmatic stream serialisation: a GEMM may begin its
+ * set-up and prefetch B while the kernel before it in the stream is still finishing.  Everything else
+ * (A, C, scratch, workspace) is only touched after that kernel has completed.  Turn it on only when the
+ * kernel that precedes a GEMM in its stream does not write that GEMM's B or s.  No counterpart in the
+ * reference. */
+int fp6m_set_launch_overlap(int enable);
+
 const char* fp6m_last_cuda_error(void);
 
 /* Library version tag, e.g. "fp6m-b200 0.1 (sm_100a)". */

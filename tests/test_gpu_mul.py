@@ -197,3 +197,41 @@ def test_full_size_against_fp32_matmul_of_dumped_operands():
         err = (torch.linalg.norm(c.float() - c_ref) / torch.linalg.norm(c_ref)).item()
         assert err <= TOL, (m, err)
     assert fm.device_status(dev) == 0
+
+
+@pytest.mark.gpu
+def test_launch_overlap_keeps_dependent_chains_exact():
+    """With programmatic dependent launch on, a GEMM starts while its predecessor drains; a chain
+    C1 = A W1, C2 = C1 W2, ... (each GEMM reads what the previous one wrote, all share one scratch and
+    one output buffer per parity) must give bit-identical results to the same chain without overlap."""
+    dev = _dev()
+    k = n = 2048
+    layers = [synth.make_layer(k, n, 256, 128, seed=20 + i, keep_dequantized=False).to(dev) for i in range(4)]
+    a0 = (synth.make_activations(16, k, 9) * 0.05).to(dev)
+    workspace = torch.zeros(n // 128 * 16, dtype=torch.int32, device=dev)
+
+    def chain():
+        bufs = [torch.zeros((16, n), dtype=torch.float16, device=dev) for _ in range(2)]
+        x = a0
+        outs = []
+        for rep in range(3):
+            for i, w in enumerate(layers):
+                y = bufs[(rep * len(layers) + i) % 2]
+                fm.mul(x, w.B, y, w.s, workspace, 256, group_size=128, layout="b200")
+                x = y
+                outs.append((y.float().abs().sum() * 0 + y.float().square().sum()).clone())
+            x = (x * 0.01).clone()      # keep the magnitudes in range between repetitions
+        torch.cuda.synchronize()
+        return torch.stack(outs), x.clone()
+
+    previous = fm.set_launch_overlap(False)
+    try:
+        ref_sums, ref_last = chain()
+        fm.set_launch_overlap(True)
+        got_sums, got_last = chain()
+    finally:
+        fm.set_launch_overlap(previous)
+    assert torch.isfinite(ref_last.float()).all()
+    assert torch.equal(ref_sums, got_sums)
+    assert torch.equal(ref_last, got_last)
+    assert fm.device_status(dev) == 0
