@@ -40,23 +40,34 @@ namespace fp6m {
 
 namespace {
 
-constexpr int kThreads = 384;          // 12 warps: W producer, MMA, A producer, (idle), 2 x 4 dequantisers
-constexpr int kDequantThreads = 256;
 constexpr int kStageW = 12288;          // packed words of one block: up to 2 x (4096 four-bit + 2048 two-bit)
 
-template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_, bool ALT_>
+template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_, int ALT_TEAMS_>
 struct Tc5Cfg {
-  // ALT: the two dequantiser teams take alternate segments (two independent chains per CTA) and keep
-  // all NT rows in registers; otherwise both teams work on every segment (one unit, half of the rows each).
-  static constexpr bool kAlt = ALT_;
+  // ALT_TEAMS > 0: that many dequantiser teams take the segments in turn (independent chains, each with
+  // its own MMA issuer) and keep all NT rows in registers; 0: two teams work on every segment (one
+  // unit and half of the rows each) behind one issuer.
+  static constexpr bool kAlt = ALT_TEAMS_ > 0;
+  static constexpr int kTeams = kAlt ? ALT_TEAMS_ : 2;
+  static constexpr int kIssuers = kAlt ? ALT_TEAMS_ : 1;
+  // warp 0: weights producer, warp 1: activations producer, warps 2.. : MMA issuers, then (from a
+  // multiple of four, so that warp % 4 is the TMEM lane quarter) four dequantiser warps per team
+  static constexpr int kDeqBase = (2 + kIssuers + 3) & ~3;
+  static constexpr int kThreads = 32 * (kDeqBase + 4 * kTeams);
+  static constexpr int kDequantThreads = 128 * kTeams;
+  // the helper warps left over below kDeqBase are further weights producers (one lane needs some 500
+  // cycles per copy it issues); the last MMA issuer, whose first MMA comes latest, also reads the epoch
+  static constexpr int kProducers = 1 + (kDeqBase - 2 - kIssuers);
+  static constexpr int kEpochWarp = 2 + kIssuers - 1;
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kStages = STAGES_;              // shared-memory stages of packed words (one block each)
   static constexpr int kRing = RING_;                  // ring of {activation tile, TMEM operand slot, accumulator tile}
   static constexpr int kCtasPerSm = CTAS_PER_SM_;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves
   static constexpr int kActBytes = 2 * kActUnitBytes;
-  static constexpr int kNumBars = 2 * kStages + (ALT_ ? 4 : 3) * kRing + 1;
-  static constexpr int kXchBytes = ALT_ ? NT * 128 * 4 : 0;   // the teams exchange half of their rows at the end of a slice
+  static constexpr int kNumBars = 2 * kStages + (kAlt ? 4 : 3) * kRing + 1;
+  static_assert(kStages >= kTeams && kRing >= kTeams, "every team needs a stage and a ring entry of its own");
+  static constexpr int kXchBytes = kAlt ? kTeams * NT * 128 * 4 : 0;   // the teams pool their partial sums at the end of a slice
   static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kXchBytes + kNumBars * 8 + 64;
   static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
@@ -240,8 +251,9 @@ struct Walk {
 };
 
 template <class C>
-__global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(const __grid_constant__ MulParams p) {
+__global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(const __grid_constant__ MulParams p) {
   constexpr int NT = C::NT, S = C::kStages, R = C::kRing;
+  constexpr int kDequantThreads = C::kDequantThreads;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* act_base = smem + S * kStageW;
   float* xch = reinterpret_cast<float*>(smem + S * kStageW + R * C::kActBytes);
@@ -280,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
     mbar_init(epoch_bar, 1);
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(misc)), "r"(C::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -290,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   const uint32_t tmem = misc[0];
   bool dead = false;
 
-  if (warp == 3 && lane == 0) {
+  if (warp == C::kEpochWarp && lane == 0) {
     // the tag of this launch's split-K partials is epoch + 1
     grid_dependency_wait();
     const uint32_t e = read_epoch_and_count(p.epochs, gridDim.x);
@@ -298,9 +310,13 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
     mbar_arrive(epoch_bar);
   }
 
-  if (warp == 0) {
-    // ================================================================== weights producer
+  if (warp == 0 || (warp >= 2 + C::kIssuers && warp < C::kDeqBase)) {
+    // ================================================================== weights producer(s)
+    // producer q of P copies the segments n = q, q + P, ... (each into stage n % S)
     if (lane == 0) {
+      constexpr int P = C::kProducers;
+      const int mine = warp == 0 ? 0 : warp - (2 + C::kIssuers) + 1;
+      int turn = 0;
       const uint64_t policy = make_evict_first_policy();
       Walk it;
       it.init(U0, U1, ups);
@@ -322,10 +338,13 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
           }
         }
         const int cnt = it.count();
-        mbar_wait_bounded<200>(empty, phase ^ 1, p.status, dead);
         const uint32_t bytes = cnt * unit_bytes;            // consecutive units are contiguous in HBM
-        mbar_arrive_expect_tx(full, bytes);
-        tma_load_1d_stream(dst, wsrc, bytes, full, policy);
+        if (P == 1 || turn == mine) {
+          mbar_wait_bounded<200>(empty, phase ^ 1, p.status, dead);
+          mbar_arrive_expect_tx(full, bytes);
+          tma_load_1d_stream(dst, wsrc, bytes, full, policy);
+        }
+        if (++turn == P) turn = 0;
         wsrc += bytes;
         dst += kStageW; full += 8; empty += 8;
         if (++stage == S) { stage = 0; phase ^= 1; dst = smem_u32(smem); full = w_full; empty = w_empty; }
@@ -333,7 +352,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
         strip_lin += new_strip;
       }
     }
-  } else if (warp == 2) {
+  } else if (warp == 1) {
     // ================================================================== activations producer
     // lane copies chunks idx = lane + 32 j of a unit: row m = idx / 8, 16-byte chunk kc = idx % 8,
     // into canonical K-major core-matrix order; everything but the K offset is loop-invariant
@@ -366,15 +385,15 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       it.next(cnt);
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp == 1 || (C::kAlt && warp == 3)) {
+  } else if (warp >= 2 && warp < 2 + C::kIssuers) {
     // ================================================================== MMA issuer(s)
     // The whole warp walks the segments and waits (warp-uniform control flow and operands); one
     // fixed lane issues the tcgen05 instructions, so that the commit tracks the MMAs before it.
     // A single thread sustains about one small MMA per 75-120 cycles, the tensor core one per 32:
     // with alternating teams each team has its own issuer (warp 1: even segments, warp 3: odd).
     {
-      constexpr int kIssuers = C::kAlt ? 2 : 1;
-      const int mine = C::kAlt ? (warp == 3) : 0;
+      constexpr int kIssuers = C::kIssuers;
+      const int mine = warp - 2;
       Walk it;
       it.init(U0, U1, ups);
       int r = 0, n = 0;
@@ -383,7 +402,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       constexpr uint32_t kStepDesc = ((NT / 8) * 256) >> 4;
       while (it.valid()) {
         const int cnt = it.count();
-        if (kIssuers == 1 || (n & 1) == mine) {
+        if (kIssuers == 1 || n == mine) {
           mbar_wait_bounded<40>(act_full + 8 * r, rphase, p.status, dead);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
           mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
@@ -400,21 +419,21 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
           }
           __syncwarp();
         }
-        ++n;
+        if (++n == kIssuers) n = 0;
         if (++r == R) { r = 0; rphase ^= 1; }
         it.next(cnt);
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= C::kDeqBase) {
     // ================================================================== dequantisers (warps 4..11)
     // Two teams of four warps; thread = weight column = TMEM lane.  A thread owns half of the rows of
     // A (rows [team NT/2, (team+1) NT/2)) when a slice is written out.
-    constexpr int HN = NT / 2;
-    const int team = (warp - 4) >> 2;
+    constexpr int HN = NT / C::kTeams;                // rows of A that a thread writes out
+    const int team = (warp - C::kDeqBase) >> 2;
     const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
     const int c = quarter * 32 + lane;               // weight column inside the strip = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    const int dtid = tid - 128;                      // 0..255 among the dequantiser threads
+    const int dtid = tid - 32 * C::kDeqBase;         // index among the dequantiser threads
     const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16
     const int strip_first = U0 / ups;
     const int row0 = team * HN;                      // this thread's rows of A and C
@@ -677,8 +696,9 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
       float acc[NT];
 #pragma unroll
       for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+      constexpr int T = C::kTeams;
       int n = team;                                  // global index of this team's next segment
-      int stage = team, r = team;                    // n % S, n % R
+      int stage = team, r = team;                    // n % S, n % R (T <= S, R)
       uint32_t wphase = 0, rphase = 0;               // (n / S) & 1, (n / R) & 1
       int n0 = 0;                                    // global index of the slice's first segment
       int strip_lin = strip_first;
@@ -717,7 +737,7 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
           pending = false;
         };
 
-        for (int j = n - n0; j < nseg; j += 2) {
+        for (int j = n - n0; j < nseg; j += T) {
           const int b = b0 + j;
           const int cnt = min(unit1, 2 * b + 2) - max(unit0, 2 * b);
           // 1.0 unless the strip has group scales; converted only when queued, so the load's latency is hidden
@@ -753,23 +773,29 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
           pr = r;
           prphase = rphase;
           pscale = __half2float(__ushort_as_half(scale_raw));
-          n += 2;
-          stage += 2;
+          n += T;
+          stage += T;
           if (stage >= S) { stage -= S; wphase ^= 1; }
-          r += 2;
+          r += T;
           if (r >= R) { r -= R; rphase ^= 1; }
         }
         if (pending) read_back();
         n0 += nseg;
         u = sl.u1;
 
-        // swap halves: rows this thread does not own go to the other team, its own rows come back
+        // pool the teams' partial sums: every thread publishes its NT rows, then sums its own HN rows
+        // over the teams in team order
         float out[HN];
 #pragma unroll
-        for (int i = 0; i < HN; ++i) xch[(team * HN + i) * kStripCols + c] = team ? acc[i] : acc[HN + i];
+        for (int m = 0; m < NT; ++m) xch[(team * NT + m) * kStripCols + c] = acc[m];
         named_bar_sync(1, kDequantThreads);
 #pragma unroll
-        for (int i = 0; i < HN; ++i) out[i] = (team ? acc[HN + i] : acc[i]) + xch[((1 - team) * HN + i) * kStripCols + c];
+        for (int i = 0; i < HN; ++i) {
+          float v = 0.f;
+#pragma unroll
+          for (int t = 0; t < T; ++t) v += xch[(t * NT + row0 + i) * kStripCols + c];
+          out[i] = v;
+        }
         named_bar_sync(1, kDequantThreads);              // the buffer may be rewritten by the next slice
         finish_slice(sl, out);
 #pragma unroll
@@ -783,14 +809,14 @@ __global__ void __launch_bounds__(kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(c
   // ---- all roles are done with tensor memory: give it back
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
   }
 }
 
-using Tc5Rows16 = Tc5Cfg<16, 7, 3, 2, true>;
-using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2, false>;
-using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2, false>;
+using Tc5Rows16 = Tc5Cfg<16, 12, 6, 1, 4>;
+using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2, 0>;
+using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2, 0>;
 
 bool g_overlap_launches = false;
 
@@ -806,7 +832,7 @@ cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.sched.ctas);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(C::kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
