@@ -50,7 +50,9 @@ extern "C" {
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
   (void)M; (void)N; (void)K; (void)quant_cols; (void)sms;
   // upper bound over every configuration: the largest grid with the largest partial tile
-  size_t b = tc5_scratch_bytes(kMaxCtas, tc5_rows_per_pass());
+  size_t b = tc5_scratch_bytes(kMaxCtas, 16);
+  const size_t w = wide_scratch_bytes(kMaxWideCtas, wide_rows_per_pass());
+  if (w > b) b = w;
   return (b + 255) & ~(size_t)255;
 }
 
@@ -84,10 +86,13 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   DeviceGuard guard(dev);
   if (sms <= 0) sms = sm_count(dev);
   if (sms <= 0) return cuda_fail(cudaGetLastError(), "cudaDeviceGetAttribute");
-  const int rows = tc5_rows_per_pass();
+  // up to 16 rows: the kernel with fp32 group scaling; more: the wide kernel, 256 rows per pass
+  const bool wide = M > 16;
+  const int rows = wide ? wide_rows_per_pass() : 16;
   const int pass_rows = M < rows ? M : rows;
-  long long want = (long long)sms * tc5_ctas_per_sm(pass_rows);
-  int ctas = want < kMaxCtas ? (int)want : kMaxCtas;
+  long long want = wide ? (long long)sms : (long long)sms * tc5_ctas_per_sm(pass_rows);
+  const int cap = wide ? kMaxWideCtas : kMaxCtas;
+  int ctas = want < cap ? (int)want : cap;
 
   MulParams p;
   p.geo = make_geometry(K, N, qc, group_size);
@@ -101,7 +106,7 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
     if (ctas > by_work) ctas = by_work;
     if (ctas > total_units) ctas = total_units;
   }
-  if (scratch_bytes < tc5_scratch_bytes(ctas, pass_rows)) return FP6M_ERR_SCRATCH;
+  if (scratch_bytes < (wide ? wide_scratch_bytes(ctas, pass_rows) : tc5_scratch_bytes(ctas, pass_rows))) return FP6M_ERR_SCRATCH;
   make_schedule(p.geo, ctas, &p.sched);
   p.B = static_cast<const uint8_t*>(B);
   p.S = static_cast<const half*>(s);
@@ -115,8 +120,8 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
     p.A = static_cast<const half*>(A) + (size_t)m0 * K;
     p.C = static_cast<half*>(C) + (size_t)m0 * N;
     p.M = (M - m0) < rows ? (M - m0) : rows;
-    cudaError_t e = launch_gemm_tc5(p, static_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return cuda_fail(e, "w46_gemm_tc5 launch");
+    cudaError_t e = wide ? launch_gemm_wide(p, static_cast<cudaStream_t>(stream)) : launch_gemm_tc5(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, wide ? "w46_gemm_wide launch" : "w46_gemm_tc5 launch");
   }
   return FP6M_OK;
 }

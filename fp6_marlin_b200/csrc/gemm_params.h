@@ -34,6 +34,13 @@ void tc5_set_overlap(bool on);
 bool tc5_get_overlap();
 cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 
+// gemm_wide.cu
+constexpr int kMaxWideCtas = 192;   // one CTA per SM
+int wide_rows_per_pass();
+int wide_tile_rows(int rows);
+size_t wide_scratch_bytes(int ctas, int rows);
+cudaError_t launch_gemm_wide(const MulParams& p, cudaStream_t stream);
+
 // dump_operands.cu
 cudaError_t launch_dump_operands(const uint8_t* B, const half* S, half* W, const Geometry& geo, cudaStream_t stream);
 

@@ -35,12 +35,11 @@
 #include "device_utils.cuh"
 #include "fp6m_layout.h"
 #include "gemm_params.h"
+#include "tc5_common.cuh"
 
 namespace fp6m {
 
 namespace {
-
-constexpr int kStageW = 12288;          // packed words of one block: up to 2 x (4096 four-bit + 2048 two-bit)
 
 template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_, int ALT_TEAMS_>
 struct Tc5Cfg {
@@ -74,180 +73,6 @@ struct Tc5Cfg {
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
   static constexpr int kSlotFloats = NT * kStripCols;
   static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-};
-
-// ---- programmatic dependent launch ---------------------------------------------------------------
-// launch_dependents: the next kernel of the stream may start launching (it runs its set-up and
-// prefetches weights while this one finishes).  grid_dependency_wait: returns once every kernel this
-// one depends on has completed and its writes are visible; without a programmatic dependency both
-// are no-ops.  Everything that earlier kernels may have written (A, C, the scratch) is only touched
-// after the wait; the weights and scales are read before it.
-__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// ---- tcgen05 wrappers -------------------------------------------------------------------------
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// The four MMAs of one 64-row unit, D[128 x N] (+)= A[128 x 16] (TMEM) * B[N x 16]^T (shared memory
-// descriptor) for K steps 0..3: the operand slot advances by 8 TMEM columns and the descriptor by
-// `step_desc` (16-byte units) per step.  `accumulate` = 0 makes the first MMA overwrite D.
-template <uint32_t kStepDesc>
-__device__ __forceinline__ void tc_mma_unit(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p, t;\n"
-      ".reg .b32 a1, a2, a3;\n"
-      ".reg .b64 d1, d2, d3;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "setp.eq.b32 t, 0, 0;\n"
-      "add.u32 a1, %1, 8;\n"
-      "add.u32 a2, %1, 16;\n"
-      "add.u32 a3, %1, 24;\n"
-      "add.u64 d1, %2, %5;\n"
-      "add.u64 d2, %2, %6;\n"
-      "add.u64 d3, %2, %7;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], d1, %3, t;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], d2, %3, t;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], d3, %3, t;\n"
-      "}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate),
-        "n"(kStepDesc), "n"(2 * kStepDesc), "n"(3 * kStepDesc)
-      : "memory");
-}
-// K-major, no swizzle: 8-row x 16-byte core matrices of 128 bytes; the two K halves of a step are
-// 128 bytes apart (leading offset), 8-row groups 256 bytes apart (stride offset).
-__device__ __forceinline__ uint64_t act_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(256 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr) : "memory");
-  tc_wait_ld();
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
-  uint32_t r[8];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr) : "memory");
-  tc_wait_ld();
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-// 16-byte asynchronous copy with zero fill when `valid` is false; completion is reported to an
-// mbarrier by cp_async_arrive below.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_relaxed_u32(const unsigned int* p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_u32(unsigned int* p, uint32_t v) {
-  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t atomic_add_relaxed_u32(unsigned int* addr, uint32_t v) {
-  uint32_t old;
-  asm volatile("atom.relaxed.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
-  return old;
-}
-__device__ __forceinline__ int atomic_add_acq_rel(int* addr, int v) {
-  int old;
-  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
-  return old;
-}
-
-// Launch epoch.  Every CTA of a launch reads the epoch word and then counts itself; the CTA that
-// completes the count knows that all have read it and advances it for the next launch (also for
-// the next replay of a captured graph).  The counting atomic takes its address through the loaded
-// value, so it cannot be performed before the load.
-__device__ __forceinline__ uint32_t read_epoch_and_count(unsigned int* words, uint32_t ctas) {
-  const uint32_t e = ld_relaxed_u32(words);
-  uint32_t zero;
-  asm volatile("and.b32 %0, %1, 0;" : "=r"(zero) : "r"(e));
-  const uint32_t arrived = atomic_add_relaxed_u32(words + 1 + zero, 1u);
-  if (arrived == ctas - 1) {
-    st_relaxed_u32(words + 1, 0u);
-    st_relaxed_u32(words, e + 1);
-  }
-  return e;
-}
-
-
-// INT4 word -> the exact integers q - 8 as fp16 pairs (rows i0,i1 | i2,i3 | i4,i5 | i6,i7): the nibble is
-// OR-ed into the mantissa of 1024 (bits 0-3) or of 64 (bits 4-7) and the constant is subtracted.
-__device__ __forceinline__ void expand_int4(uint32_t q, uint32_t* b) {
-  constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
-  const half2 lo_bias = u32_as_h2(0x64086408u);   // 1032
-  const half2 hi_bias = u32_as_h2(0x54805480u);   // 72
-  b[0] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x000f000fu, 0x64006400u)), lo_bias));
-  b[1] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x00f000f0u, 0x54005400u)), hi_bias));
-  q >>= 8;
-  b[2] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x000f000fu, 0x64006400u)), lo_bias));
-  b[3] = h2_as_u32(__hsub2(u32_as_h2(lop3<kAndOr>(q, 0x00f000f0u, 0x54005400u)), hi_bias));
-}
-// FP6 four-bit word + two-bit word -> `s 00eee mm 00000000` fp16 patterns (value / 4096).
-__device__ __forceinline__ void expand_fp6(uint32_t four, uint32_t two, int rot, uint32_t* b) {
-  constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;
-  const uint32_t r0 = __funnelshift_l(two, two, rot) & 0x90909090u;
-  const uint32_t r1 = __funnelshift_l(two, two, rot + 2) & 0x90909090u;
-  const uint32_t x0 = lop3<kAndOr>(four, 0x0f0f0f0fu, r0);
-  const uint32_t x1 = lop3<kAndOr>(four >> 4, 0x0f0f0f0fu, r1);
-  b[0] = prmt(x0, 0u, 0x1404u);
-  b[1] = prmt(x0, 0u, 0x3424u);
-  b[2] = prmt(x1, 0u, 0x1404u);
-  b[3] = prmt(x1, 0u, 0x3424u);
-}
-
-// Walks the units [u0, u1) of a CTA as SEGMENTS: runs of one or two units inside one 128-row block
-// of one strip (= one INT4 scale group, one TMA copy, one operand slot, one accumulator tile).
-// Every role runs the same walk, so ring positions agree without communication.
-struct Walk {
-  int u, end, ups;
-  int unit, unit1;                 // position inside the strip, end of this CTA's slice of the strip
-  __device__ __forceinline__ void open_slice() { unit1 = min(ups, unit + end - u); }
-  __device__ __forceinline__ void init(int u0, int u1, int ups_) {
-    u = u0; end = u1; ups = ups_;
-    unit = u % ups;
-    open_slice();
-  }
-  __device__ __forceinline__ bool valid() const { return u < end; }
-  __device__ __forceinline__ int count() const { return ((unit & 1) == 0 && unit + 1 < unit1) ? 2 : 1; }
-  // returns true when the step left the strip
-  __device__ __forceinline__ bool next(int cnt) {
-    u += cnt;
-    unit += cnt;
-    if (unit != ups) return false;
-    unit = 0;
-    open_slice();
-    return true;
-  }
 };
 
 template <class C>

@@ -1,0 +1,518 @@
+// W(4&6)A16 GEMM on tcgen05 + TMEM for 17 to 256 rows of A per pass.
+//
+// As in the kernel for up to 16 rows (gemm_tc5.cu) the product is computed transposed: the 128 weight
+// columns of a strip are the M dimension of tcgen05.mma (one TMEM lane per column), the rows of A its
+// N dimension (32 ... 256), the dequantised weights the A operand in TENSOR MEMORY.  Differences:
+//   * The INT4 group scale is multiplied into the operand - fp16(q - 8) * s_g with one fp16 rounding,
+//     bit for bit the dequantised weight of the reference's rule (test.py:98) - so ONE accumulator
+//     tile collects a whole slice of K and is read back once per slice, not once per scale group.
+//     Per-channel INT4 scales and FP6 scales (times 4096) are applied to the fp32 sums, as before.
+//   * The activations come by tiled TMA: one copy per 64-row unit brings NT rows x 64 halves (128-byte
+//     rows, 128-byte swizzle) - the K-major swizzled operand layout of tcgen05 with 1024 bytes between
+//     8-row groups; a K step of 16 advances the descriptor by 32 bytes.  Rows beyond M are zero-filled
+//     by the copy engine.
+//   * One thread issues all MMAs in segment order, so the summation order is fixed.
+// One CTA per SM: warp 0 weights producer, warp 1 activations producer, warp 2 MMA issuer (and TMEM
+// owner), warp 3 launch epoch, then four dequantiser warps per team; teams take the segments in turn.
+// Split-K between CTAs uses the tagged slots of gemm_tc5.cu (the strip's last contributor reduces).
+//
+// Replaces the reference's large-tile path (thread_m_blocks 2..4 and its `parallel` batches,
+// fp6_marlin/fp6_marlin_cuda_kernel.cu:864-951).
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "device_utils.cuh"
+#include "fp6m_layout.h"
+#include "gemm_params.h"
+#include "tc5_common.cuh"
+
+namespace fp6m {
+
+namespace {
+
+template <int NT_, int TEAMS_, int STAGES_, int ACT_STAGES_, int RING_>
+struct WideCfg {
+  static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
+  static constexpr int kTeams = TEAMS_;
+  static constexpr int kStages = STAGES_;              // weight stages (one segment = up to two units each)
+  static constexpr int kActStages = ACT_STAGES_;       // activation stages (one unit each)
+  static constexpr int kRing = RING_;                  // TMEM operand slots (one segment each)
+  static constexpr int kDeqBase = 4;
+  static constexpr int kThreads = 32 * (kDeqBase + 4 * kTeams);
+  static constexpr int kDequantThreads = 128 * kTeams;
+  static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves, 1024-byte aligned stages
+  static constexpr int kNumBars = 2 * kStages + 2 * kActStages + 2 * kRing + 3;
+  static constexpr int kSmemBytes = kStages * kStageW + kActStages * kActUnitBytes + kNumBars * 8 + 64 + 1024;
+  static constexpr int kTmemD = 0, kTmemA = NT;        // the accumulator tile, then operand slots of 64 columns
+  static constexpr int kTmemUsed = kTmemA + kRing * 64;
+  static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
+  static constexpr int kSlotWords = NT * kStripCols;
+  static constexpr int kRowsPerTeam = NT / kTeams;     // rows of the accumulator tile a team writes out
+  static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  static_assert(kTmemUsed <= 512 && kRowsPerTeam % 16 == 0 && kStages >= kTeams && kRing >= kTeams, "configuration");
+};
+
+// activations of one unit: K-major, 128-byte swizzle (layout type 2), 1024 bytes between 8-row groups;
+// the leading-dimension field is not used by swizzled K-major layouts
+__device__ __forceinline__ uint64_t wide_act_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
+__device__ __forceinline__ void tma_load_act(uint32_t dst, const CUtensorMap* map, int k0, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(k0), "r"(0), "r"(bar) : "memory");
+}
+// INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
+__device__ __forceinline__ void expand_int4_scaled(uint32_t q, half2 s, uint32_t* b) {
+  uint32_t e[4];
+  expand_int4(q, e);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = h2_as_u32(__hmul2(u32_as_h2(e[i]), s));
+}
+
+template <class C>
+__global__ void __launch_bounds__(C::kThreads, 1)
+w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant__ CUtensorMap amap) {
+  constexpr int NT = C::NT, S = C::kStages, RA = C::kActStages, R = C::kRing, T = C::kTeams;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* act_base = smem + S * kStageW;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(act_base + RA * C::kActUnitBytes);
+  uint32_t* misc = reinterpret_cast<uint32_t*>(bars + C::kNumBars);   // [0] TMEM base, [1] launch epoch
+  const uint32_t w_full = smem_u32(bars), w_empty = w_full + 8 * S;
+  const uint32_t a_full = w_empty + 8 * S, a_empty = a_full + 8 * RA;
+  const uint32_t ready = a_empty + 8 * RA, slot_free = ready + 8 * R;
+  const uint32_t slice_done = slot_free + 8 * R, d_read = slice_done + 8, epoch_bar = d_read + 8;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cta = blockIdx.x;
+  const Geometry& geo = p.geo;
+  const int ups = units_per_strip(geo);
+  const int U0 = p.sched.bound[cta], U1 = p.sched.bound[cta + 1];
+  launch_dependents();
+  if (U0 >= U1) {                      // no work: still counted, see read_epoch_and_count
+    if (tid == 0) {
+      grid_dependency_wait();
+      read_epoch_and_count(p.epochs, gridDim.x);
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(w_full + 8 * s, 1);      // the expect_tx arrival of the weights producer
+      mbar_init(w_empty + 8 * s, 4);     // the team that read the stage has its words in registers
+    }
+    for (int s = 0; s < RA; ++s) {
+      mbar_init(a_full + 8 * s, 1);      // the expect_tx arrival of the activations producer
+      mbar_init(a_empty + 8 * s, 1);     // tcgen05.commit: the MMAs that read the stage have finished
+    }
+    for (int r = 0; r < R; ++r) {
+      mbar_init(ready + 8 * r, 4);       // the segment's team stored the operands into TMEM
+      mbar_init(slot_free + 8 * r, 1);   // tcgen05.commit: the MMAs that read the slot have finished
+    }
+    mbar_init(slice_done, 1);            // tcgen05.commit: the accumulator tile holds the whole slice
+    mbar_init(d_read, 4 * T);            // every dequantiser warp has read its part of the tile back
+    mbar_init(epoch_bar, 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(misc)), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = misc[0];
+  bool dead = false;
+
+  if (warp == 0) {
+    // ================================================================== weights producer
+    if (lane == 0) {
+      const uint64_t policy = make_evict_first_policy();
+      Walk it;
+      it.init(U0, U1, ups);
+      bool new_strip = true;
+      int strip_lin = U0 / ups;
+      const uint8_t* wsrc = nullptr;
+      uint32_t unit_bytes = 0;
+      int stage = 0;
+      uint32_t phase = 0;
+      while (it.valid()) {
+        if (new_strip) {
+          if (strip_lin < geo.strips4) {
+            unit_bytes = strip_quads(geo.n4, strip_lin) * kInt4UnitQuadBytes;
+            wsrc = p.B + int4_unit_offset(geo, strip_lin, 0) + (size_t)it.unit * unit_bytes;
+          } else {
+            unit_bytes = strip_quads(geo.n6, strip_lin - geo.strips4) * kFp6UnitQuadBytes;
+            wsrc = p.B + fp6_unit_offset(geo, strip_lin - geo.strips4, 0) + (size_t)it.unit * unit_bytes;
+          }
+        }
+        const int cnt = it.count();
+        const uint32_t bytes = cnt * unit_bytes;            // consecutive units are contiguous in HBM
+        mbar_wait_bounded<200>(w_empty + 8 * stage, phase ^ 1, p.status, dead);
+        mbar_arrive_expect_tx(w_full + 8 * stage, bytes);
+        tma_load_1d_stream(smem_u32(smem) + stage * kStageW, wsrc, bytes, w_full + 8 * stage, policy);
+        wsrc += bytes;
+        if (++stage == S) { stage = 0; phase ^= 1; }
+        new_strip = it.next(cnt);
+        strip_lin += new_strip;
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================== activations producer
+    if (lane == 0) {
+      Walk it;
+      it.init(U0, U1, ups);
+      int sa = 0;
+      uint32_t aphase = 0;
+      grid_dependency_wait();                           // A may come from the previous kernel
+      while (it.valid()) {
+        const int cnt = it.count();
+        for (int h = 0; h < cnt; ++h) {
+          mbar_wait_bounded<100>(a_empty + 8 * sa, aphase ^ 1, p.status, dead);
+          mbar_arrive_expect_tx(a_full + 8 * sa, C::kActUnitBytes);
+          tma_load_act(smem_u32(act_base) + sa * C::kActUnitBytes, &amap, (it.unit + h) * kUnitRows, a_full + 8 * sa);
+          if (++sa == RA) { sa = 0; aphase ^= 1; }
+        }
+        it.next(cnt);
+      }
+    }
+  } else if (warp == 2) {
+    // ================================================================== MMA issuer
+    // The whole warp walks the segments and waits; one fixed lane issues, so the commits track its MMAs.
+    Walk it;
+    it.init(U0, U1, ups);
+    int r = 0, sa = 0, slices = 0;
+    uint32_t rphase = 0, aphase = 0;
+    bool first = true;                                // next MMA is the first of a slice: it overwrites the tile
+    constexpr uint32_t kStepDesc = 32 >> 4;            // 16 halves along a 128-byte row
+    const uint64_t desc0 = wide_act_desc(smem_u32(act_base));
+    while (it.valid()) {
+      const int cnt = it.count();
+      mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
+      if (first && slices > 0) mbar_wait_bounded<40>(d_read, (slices - 1) & 1, p.status, dead);   // previous slice was read back
+      const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
+      for (int h = 0; h < cnt; ++h) {
+        mbar_wait_bounded<40>(a_full + 8 * sa, aphase, p.status, dead);
+        tc_fence_after();
+        // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
+        const uint64_t desc = desc0 + (uint64_t)(sa * (C::kActUnitBytes >> 4));
+        if (lane == 0) {
+          tc_mma_unit<kStepDesc>(tmem + C::kTmemD, a_tmem + h * 32, desc, C::kIdesc, first ? 0u : 1u);
+          tc_commit(a_empty + 8 * sa);                  // the stage may be refilled when these MMAs are done
+        }
+        __syncwarp();
+        first = false;
+        if (++sa == RA) { sa = 0; aphase ^= 1; }
+      }
+      const bool slice_ends = it.next(cnt) || !it.valid();
+      if (lane == 0) {
+        tc_commit(slot_free + 8 * r);
+        if (slice_ends) tc_commit(slice_done);
+      }
+      __syncwarp();
+      if (slice_ends) { first = true; ++slices; }
+      if (++r == R) { r = 0; rphase ^= 1; }
+    }
+  } else if (warp == 3) {
+    if (lane == 0) {
+      // the tag of this launch's split-K partials is epoch + 1
+      grid_dependency_wait();
+      const uint32_t e = read_epoch_and_count(p.epochs, gridDim.x);
+      misc[1] = e;
+      mbar_arrive(epoch_bar);
+    }
+  } else {
+    // ================================================================== dequantisers (warps 4..)
+    // thread = weight column = TMEM lane; team t expands the segments n = t, t + T, ... of the CTA
+    // and writes out rows [t NT/T, (t+1) NT/T) of every slice's accumulator tile
+    constexpr int RPT = C::kRowsPerTeam;
+    const int team = (warp - C::kDeqBase) >> 2;
+    const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
+    const int c = quarter * 32 + lane;               // weight column inside the strip
+    const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t a_base = lane_base + C::kTmemA;
+    const uint32_t d_base = lane_base + C::kTmemD + team * RPT;
+    const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16
+    const int strip_first = U0 / ups;
+    const int row0 = team * RPT;
+
+    struct Slice {
+      int strip_lin, strip, nq, u0, u1, s_begin;
+      bool is6, group;
+    };
+    auto open_slice = [&](int strip_lin, int u) {
+      Slice sl;
+      sl.strip_lin = strip_lin;
+      sl.is6 = strip_lin >= geo.strips4;
+      sl.strip = sl.is6 ? strip_lin - geo.strips4 : strip_lin;
+      sl.nq = strip_quads(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      sl.group = !sl.is6 && geo.groups > 1;
+      sl.s_begin = strip_lin * ups;
+      sl.u0 = u;
+      sl.u1 = min(U1, sl.s_begin + ups);
+      return sl;
+    };
+    auto column_scale = [&](const Slice& sl, bool writes) {
+      float col_scale = 1.f;      // per-channel INT4: s; FP6: s * 4096; group INT4: already in the operands
+      if (writes && !sl.group) {
+        const half* sp = p.S + (sl.is6 ? fp6_scale_offset(geo, sl.strip) : int4_scale_offset(geo, sl.strip, 0));
+        col_scale = __half2float(__ldg(sp + c)) * (sl.is6 ? 4096.f : 1.f);
+      }
+      return col_scale;
+    };
+    auto slot_of = [&](int cc, int strip_lin) {
+      // slot 0 holds the partial of a CTA's first strip, slot 1 that of its last strip
+      const int cc_first = p.sched.bound[cc] / ups;
+      return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotWords + row0 * kStripCols + c;
+    };
+    auto store_rows = [&](const Slice& sl, int m0, const float (&v)[16], float col_scale, bool writes) {
+      const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
+      if (writes) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (row0 + m0 + i < p.M) p.C[(size_t)(row0 + m0 + i) * p.N + gcol] = __float2half_rn(v[i] * col_scale);
+      }
+    };
+
+    int reduce_strip = -1;                           // strip this CTA must reduce at its end
+    uint32_t reduce_tag = 0;
+    int n = team, stage = team, r = team;            // this team's next segment, its weight stage and operand slot
+    uint32_t wphase = 0, rphase = 0;
+    int n0 = 0, slices = 0;
+    int strip_lin = strip_first;
+    int u = U0;
+    while (u < U1) {
+      const Slice sl = open_slice(strip_lin, u);
+      const bool is6 = sl.is6;
+      const bool col_live = c < sl.nq * kQuadCols;     // padded quads of a ragged strip hold no data
+      const uint32_t unit_bytes = sl.nq * (is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
+      const int unit0 = u - sl.s_begin, unit1 = sl.u1 - sl.s_begin;
+      const int b0 = unit0 >> 1;                        // first 128-row block of the slice
+      const int nseg = ((unit1 + 1) >> 1) - b0;         // one segment per block that the slice touches
+      const uint32_t two_off = sl.nq * kInt4UnitQuadBytes + c * 16;
+      const int scale_stride = sl.nq * kQuadCols;
+      const half* sp0 = p.S + (sl.group ? int4_scale_offset(geo, sl.strip, 0) + c : 0);
+      const bool scaled = sl.group && col_live;
+      half next_scale = __float2half(1.f);
+      if (scaled && n - n0 < nseg) next_scale = __ldg(sp0 + (size_t)(b0 + n - n0) * scale_stride);
+
+      for (int j = n - n0; j < nseg; j += T) {
+        const int b = b0 + j;
+        const int cnt = min(unit1, 2 * b + 2) - max(unit0, 2 * b);
+        const half2 s2 = __half2half2(next_scale);
+        if (scaled && j + T < nseg) next_scale = __ldg(sp0 + (size_t)(b + T) * scale_stride);   // used one iteration later
+        mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
+        const uint8_t* st = smem + stage * kStageW;
+        // the MMAs that read this operand slot R segments ago have finished
+        mbar_wait_bounded(slot_free + 8 * r, rphase ^ 1, p.status, dead);
+        tc_fence_after();
+        const uint32_t a_tmem = a_base + r * 64;
+#pragma unroll 1
+        for (int h = 0; h < cnt; ++h) {
+          // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
+          const uint8_t* su = st + h * unit_bytes;
+          const uint4 lo = *reinterpret_cast<const uint4*>(su + lds_lo);          // words 0..3
+          const uint4 hi = *reinterpret_cast<const uint4*>(su + (lds_lo ^ 16));   // words 4..7
+          uint4 two = make_uint4(0, 0, 0, 0);
+          if (is6) two = *reinterpret_cast<const uint4*>(su + two_off);
+          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
+#pragma unroll
+          for (int step = 0; step < 4; ++step) {
+            uint32_t regs[8];
+            if (is6) {
+              expand_fp6(words[2 * step], twos[step], 0, regs);
+              expand_fp6(words[2 * step + 1], twos[step], 4, regs + 4);
+            } else if (sl.group) {
+              expand_int4_scaled(words[2 * step], s2, regs);
+              expand_int4_scaled(words[2 * step + 1], s2, regs + 4);
+            } else {
+              expand_int4(words[2 * step], regs);
+              expand_int4(words[2 * step + 1], regs + 4);
+            }
+            tc_st8(a_tmem + h * 32 + step * 8, regs);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
+        tc_wait_st();
+        tc_fence_before();
+        if (lane == 0) mbar_arrive(ready + 8 * r);
+        n += T;
+        stage += T;
+        if (stage >= S) { stage -= S; wphase ^= 1; }
+        r += T;
+        if (r >= R) { r -= R; rphase ^= 1; }
+      }
+      n0 += nseg;
+      u = sl.u1;
+
+      // ---------------- the slice is in the accumulator tile: write C, or store a tagged partial
+      mbar_wait_bounded(slice_done, slices & 1, p.status, dead);
+      tc_fence_after();
+      grid_dependency_wait();                        // C and the scratch may still be in use by the previous kernel
+      const bool whole = sl.u0 == sl.s_begin && sl.u1 == sl.s_begin + ups;
+      const bool writes = c < strip_cols(is6 ? geo.n6 : geo.n4, sl.strip);
+      const float col_scale = whole ? column_scale(sl, writes) : 1.f;
+      uint32_t tag = 0;
+      unsigned long long* slot = nullptr;
+      if (!whole) {
+        mbar_wait_bounded(epoch_bar, 0, p.status, dead);   // completed long ago: orders the read of misc[1]
+        tag = misc[1] + 1;
+        slot = slot_of(cta, sl.strip_lin);
+      }
+#pragma unroll 1
+      for (int m0 = 0; m0 < RPT; m0 += 16) {
+        float v[16];
+        tc_ld16(d_base + m0, v);
+        if (whole) {
+          store_rows(sl, m0, v, col_scale, writes);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            st_relaxed_u64(slot + (m0 + i) * kStripCols, ((unsigned long long)tag << 32) | __float_as_uint(v[i]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_read);            // the MMA issuer may start the next slice in the tile
+      if (!whole && sl.u1 == sl.s_begin + ups) {     // last contributor of the strip: reduce it at the end
+        reduce_strip = sl.strip_lin;
+        reduce_tag = tag;
+      }
+      ++slices;
+      ++strip_lin;
+    }
+
+    // ---------------- after the last slice: reduce the strip whose last contributor this CTA is, by
+    // reading the tagged slots of the lower-numbered contributors (bounded spin) in CTA order
+    if (reduce_strip >= 0) {
+      const Slice sl = open_slice(reduce_strip, 0);
+      int c_lo = cta;
+      while (c_lo > 0 && p.sched.bound[c_lo] > sl.s_begin) --c_lo;
+      const bool writes = c < strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      const float col_scale = column_scale(sl, writes);
+#pragma unroll 1
+      for (int m0 = 0; m0 < RPT; m0 += 16) {
+        float sum[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+        for (int cc = c_lo; cc <= cta; ++cc) {
+          if (p.sched.bound[cc] >= p.sched.bound[cc + 1]) continue;
+          const unsigned long long* src = slot_of(cc, reduce_strip) + m0 * kStripCols;
+          unsigned long long v[16];
+          bool all_here = false;
+#pragma unroll 1
+          for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = ld_relaxed_u64(src + i * kStripCols);
+            all_here = true;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) all_here = all_here && (uint32_t)(v[i] >> 32) == reduce_tag;
+            if (dead) break;
+          }
+          if (!all_here && !dead) {
+            dead = true;
+            if (p.status) atomicExch(p.status, kStatusTimeout);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sum[i] += __uint_as_float((uint32_t)v[i]);
+        }
+        store_rows(sl, m0, sum, col_scale, writes);
+      }
+    }
+  }
+
+  // ---- all roles are done with tensor memory: give it back
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+using Wide32 = WideCfg<32, 2, 8, 8, 4>;
+using Wide64 = WideCfg<64, 4, 8, 8, 4>;
+using Wide128 = WideCfg<128, 2, 6, 6, 3>;
+using Wide256 = WideCfg<256, 2, 4, 4, 3>;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up once through the runtime (no link against libcuda).
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+template <class C>
+cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
+  // A as a K x M tensor (K contiguous): one box = 64 halves x NT rows = the activations of one 64-row unit
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return cudaErrorNotSupported;
+  alignas(64) CUtensorMap amap;
+  const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+  const cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)C::NT};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(p.A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w46_gemm_wide_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.sched.ctas);
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w46_gemm_wide_kernel<C>, p, amap);
+}
+
+}  // namespace
+
+int wide_rows_per_pass() { return 256; }
+
+// rows of the MMA tile used for `rows` rows of A
+int wide_tile_rows(int rows) { return rows <= 32 ? 32 : (rows <= 64 ? 64 : (rows <= 128 ? 128 : 256)); }
+
+size_t wide_scratch_bytes(int ctas, int rows) {
+  return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * wide_tile_rows(rows) * kStripCols * sizeof(unsigned long long);
+}
+
+// Runs the GEMM for rows [0, p.M) with 16 < p.M <= 256; the host dispatcher loops over larger M.
+cudaError_t launch_gemm_wide(const MulParams& p, cudaStream_t stream) {
+  const bool overlap = tc5_get_overlap();
+  switch (wide_tile_rows(p.M)) {
+    case 32: return launch_wide<Wide32>(p, stream, overlap);
+    case 64: return launch_wide<Wide64>(p, stream, overlap);
+    case 128: return launch_wide<Wide128>(p, stream, overlap);
+    default: return launch_wide<Wide256>(p, stream, overlap);
+  }
+}
+
+}  // namespace fp6m

@@ -235,3 +235,38 @@ def test_launch_overlap_keeps_dependent_chains_exact():
     assert torch.equal(ref_sums, got_sums)
     assert torch.equal(ref_last, got_last)
     assert fm.device_status(dev) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [17, 33, 100, 129, 256, 257, 300, 700])
+def test_wide_tiles_and_passes(m):
+    """More than 16 rows: MMA tiles of 32/64/128/256 rows, ragged last tile, several passes of 256 rows."""
+    for (k, n, qc, gs) in [(1024, 2048, 256, 128), (512, 1280, 256, -1), (2048, 768, -1, 128)]:
+        err, _ = _run(m, k, n, qc, gs, 64, 256, seed=m)
+        assert err <= TOL, (m, k, n, qc, gs, err)
+
+
+@pytest.mark.gpu
+def test_wide_one_hot_rows_reproduce_scaled_weights_exactly():
+    """With group scales the wide kernel feeds fp16((q - 8) * s_g) to the tensor cores: one-hot rows of A
+    must return exactly the oracle's dequantised weights (the fp32 sum has a single term)."""
+    dev = _dev()
+    k, n, qc, gs = 256, 512, 256, 128
+    w = synth.make_weight_fp16(k, n, qc, seed=5)
+    ww = fm.make_w46_weight(w, qc, gs, keep_dequantized=False).to(dev)
+    a = torch.eye(k, dtype=torch.float16)[:200].contiguous().to(dev)       # rows 0..199 of the identity
+    c = torch.zeros((200, n), dtype=torch.float16, device=dev)
+    workspace = torch.zeros(max(n // 128 * 16, 16), dtype=torch.int32, device=dev)
+    fm.mul(a, ww.B, c, ww.s, workspace, qc, 64, 256, group_size=gs, layout="b200")
+    torch.cuda.synchronize()
+    expect = _oracle_weight(w, qc, gs)[:200]
+    assert np.array_equal(c.cpu().numpy().view(np.uint16), expect.view(np.uint16))
+
+
+@pytest.mark.gpu
+def test_wide_long_k_and_split_strips():
+    """K = 8192 with few strips: every strip is shared by several CTAs (tagged split-K slots of 256 rows)."""
+    err, _ = _run(256, 8192, 1024, 256, 128, 64, 256, seed=3)
+    assert err <= TOL, err
+    err, _ = _run(40, 8192, 512, -1, 128, 64, 256, seed=4)
+    assert err <= TOL, err
