@@ -27,7 +27,6 @@ struct MulParams {
 constexpr int kEpochWords = 64;     // scratch header size in 32-bit words
 
 // gemm_tc5.cu
-int tc5_rows_per_pass();
 int tc5_ctas_per_sm(int rows);
 size_t tc5_scratch_bytes(int ctas, int rows);
 void tc5_set_overlap(bool on);

@@ -1,32 +1,37 @@
-// W(4&6)A16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for up to 64 rows of A per pass.
+// W(4&6)A16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for up to 16 rows of A.
 //
 // The product is computed transposed, D[n, m] = sum_k W[k, n] * A[m, k]: the 128 weight columns of
 // a strip are the M dimension of tcgen05.mma (one TMEM lane per weight column), the rows of A are
-// its N dimension (16, 32 or 64), and the dequantised weights are the A operand read from TENSOR
-// MEMORY, so they never travel through shared memory.  Legacy mma.sync costs about 32 cycles per
-// m16n8k16 tile on B200 and cannot keep up with HBM (profiles/w46_gemm_mma_*); tcgen05 can.
+// its N dimension (16), and the dequantised weights are the A operand read from TENSOR MEMORY, so
+// they never travel through shared memory.  Legacy mma.sync costs about 32 cycles per m16n8k16
+// tile on B200 and cannot keep up with HBM (profiles/w46_gemm_mma_*); tcgen05 can.
 //
-// One CTA = seven warps:
-//   warp 0      weights producer: one bulk TMA copy (cp.async.bulk, mbarrier completion) per
-//               SEGMENT = the one or two 64-row units of a 128-row block that belong to the CTA.
-//   warp 6      activations producer: cp.async copies that lay the segment's activations out as
+// One CTA per SM, 24 warps:
+//   warp 0, 6, 7  weights producers: one bulk TMA copy (cp.async.bulk, mbarrier completion) per
+//               SEGMENT = the one or two 64-row units of a 128-row block that belong to the CTA;
+//               a single lane needs ~500 cycles per copy, so the segments are dealt round robin.
+//   warp 1      activations producer: cp.async copies that lay the segment's activations out as
 //               canonical K-major 8x16-byte core matrices (the B operand of the MMA).
-//   warp 1      one lane issues tcgen05.mma (kind::f16, fp32 accumulators in TMEM) and commits
-//               completion to mbarriers; the warp also owns the TMEM allocation.
-//   warps 2-5   dequantisers: thread = weight column = TMEM lane.  A thread reads its 32 bytes of
-//               a unit, expands the eight words in registers and stores them with tcgen05.st into
-//               a ring of TMEM operand slots.  INT4 nibbles become the exact integers q - 8 in fp16
-//               (OR into 1024 + q / 64 + q, then subtract 1032 / 72) - bit for bit what the
-//               reference's dequant_8int4 feeds its tensor cores (fp6_marlin_cuda_kernel.cu:249-286).
-//               FP6 codes become `s 00eee mm` fp16 patterns (exact value / 4096, as dequant_8fp6
-//               builds them before its multiply by 4096, :195-237).  After every scale
-//               group (128 rows) the same threads read the accumulator tile back (tcgen05.ld),
-//               multiply by their column's group scale in fp32 and add to registers; every ring
-//               position has its own accumulator tile and the read-back runs one or two segments
-//               late, so it never waits for the tensor core.
-// Work comes from the byte-weighted stripe schedule (fp6m_layout.h); strips shared by several CTAs
-// are reduced through fp32 scratch slots by the last CTA to arrive (one acq_rel atomic on a counter
-// in the caller's workspace) - no CTA waits for another, every wait in the kernel is bounded.
+//   warps 2-5   MMA issuers, one per dequantiser team: one lane issues tcgen05.mma (kind::f16, fp32
+//               accumulators in TMEM) for its team's segments and commits completion to mbarriers.
+//               A thread sustains one small MMA per 75-120 cycles, the tensor core one per 32.
+//               Warp 2 owns the TMEM allocation; warp 5 also reads the launch epoch.
+//   warps 8-23  four dequantiser TEAMS of four warps; thread = weight column = TMEM lane.  The teams
+//               take the CTA's segments in turn (independent chains that hide each other's
+//               latencies).  A thread reads its 32 bytes of a unit, expands the eight words in
+//               registers and stores them with tcgen05.st into the segment's TMEM operand slot.  INT4
+//               nibbles become the exact integers q - 8 in fp16 (OR into 1024 + q / 64 + q, then
+//               subtract 1032 / 72) - bit for bit what the reference's dequant_8int4 feeds its tensor
+//               cores (fp6_marlin_cuda_kernel.cu:249-286).  FP6 codes become `s 00eee mm` fp16 patterns
+//               (exact value / 4096, as dequant_8fp6 builds them before its multiply by 4096,
+//               :195-237).  Every segment has its own accumulator tile; after storing its next
+//               segment a team reads the previous one's tile back (tcgen05.ld), multiplies by the
+//               column's group scale in fp32 and adds to registers.  At the end of a slice (the CTA's
+//               units of one strip) the teams pool their sums through shared memory.
+// Work comes from the byte-weighted stripe schedule (fp6m_layout.h).  Strips shared by several CTAs
+// are reduced without atomics or fences on the data path: partials are stored as {value, tag} 64-bit
+// words, the tag being a per-launch epoch, and the strip's last contributor (in CTA order) sums the
+// slots at its end - it only ever waits, with a bound, for lower-numbered CTAs.
 //
 // Replaces the reference's fp6_kernel_marlin (fp6_marlin/fp6_marlin_cuda_kernel.cu:288-837).
 #include <cuda_fp16.h>
@@ -41,14 +46,12 @@ namespace fp6m {
 
 namespace {
 
-template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_, int ALT_TEAMS_>
+template <int NT_, int STAGES_, int RING_, int CTAS_PER_SM_, int TEAMS_>
 struct Tc5Cfg {
-  // ALT_TEAMS > 0: that many dequantiser teams take the segments in turn (independent chains, each with
-  // its own MMA issuer) and keep all NT rows in registers; 0: two teams work on every segment (one
-  // unit and half of the rows each) behind one issuer.
-  static constexpr bool kAlt = ALT_TEAMS_ > 0;
-  static constexpr int kTeams = kAlt ? ALT_TEAMS_ : 2;
-  static constexpr int kIssuers = kAlt ? ALT_TEAMS_ : 1;
+  // TEAMS dequantiser teams take the segments in turn (independent chains, each with its own MMA
+  // issuer) and keep all NT rows in registers
+  static constexpr int kTeams = TEAMS_;
+  static constexpr int kIssuers = TEAMS_;
   // warp 0: weights producer, warp 1: activations producer, warps 2.. : MMA issuers, then (from a
   // multiple of four, so that warp % 4 is the TMEM lane quarter) four dequantiser warps per team
   static constexpr int kDeqBase = (2 + kIssuers + 3) & ~3;
@@ -64,9 +67,9 @@ struct Tc5Cfg {
   static constexpr int kCtasPerSm = CTAS_PER_SM_;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves
   static constexpr int kActBytes = 2 * kActUnitBytes;
-  static constexpr int kNumBars = 2 * kStages + (kAlt ? 4 : 3) * kRing + 1;
+  static constexpr int kNumBars = 2 * kStages + 4 * kRing + 1;
   static_assert(kStages >= kTeams && kRing >= kTeams, "every team needs a stage and a ring entry of its own");
-  static constexpr int kXchBytes = kAlt ? kTeams * NT * 128 * 4 : 0;   // the teams pool their partial sums at the end of a slice
+  static constexpr int kXchBytes = kTeams * NT * 128 * 4;   // the teams pool their partial sums at the end of a slice
   static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kXchBytes + kNumBars * 8 + 64;
   static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
   uint32_t* misc = reinterpret_cast<uint32_t*>(bars + C::kNumBars);   // [0] TMEM base, [1] flag
   const uint32_t w_full = smem_u32(bars), w_empty = w_full + 8 * S;
   const uint32_t act_full = w_empty + 8 * S, ready = act_full + 8 * R, done = ready + 8 * R;
-  const uint32_t d_free = done + 8 * R;    // ALT only: the accumulator tile has been read back
+  const uint32_t d_free = done + 8 * R;    // the accumulator tile has been read back
   const uint32_t epoch_bar = smem_u32(bars + C::kNumBars - 1);   // misc[1] holds the launch epoch
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -106,12 +109,12 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(w_full + 8 * s, 1);      // the expect_tx arrival of the weights producer
-      mbar_init(w_empty + 8 * s, C::kAlt ? 4 : 8);   // the dequantiser warps that read the stage have its words in registers
+      mbar_init(w_empty + 8 * s, 4);     // the team that read the stage has its words in registers
     }
     for (int r = 0; r < R; ++r) {
       mbar_init(act_full + 8 * r, 32);   // cp.async completions of the 32 lanes of the activation producer
-      mbar_init(ready + 8 * r, C::kAlt ? 4 : 8);     // the dequantiser warps of the segment stored the operands into TMEM
-      if (C::kAlt) mbar_init(d_free + 8 * r, 4);     // the team that owns the segment has read the accumulator tile back
+      mbar_init(ready + 8 * r, 4);       // the segment's team stored the operands into TMEM
+      mbar_init(d_free + 8 * r, 4);          // the team that owns the segment has read the accumulator tile back
       mbar_init(done + 8 * r, 1);        // tcgen05.commit: every MMA of the segment has finished
     }
     mbar_init(epoch_bar, 1);
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
           mbar_wait_bounded<40>(act_full + 8 * r, rphase, p.status, dead);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
           mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
-          if (C::kAlt) mbar_wait_bounded(d_free + 8 * r, rphase ^ 1, p.status, dead);   // previous tile of this entry was read
+          mbar_wait_bounded(d_free + 8 * r, rphase ^ 1, p.status, dead);   // previous tile of this entry was read
           tc_fence_after();
           const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
           const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
@@ -282,8 +285,9 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
 
     // ---------------- the strip is finished for this CTA: write C, or store a partial sum
     // Split-K without atomics or fences: a partial is stored as 64-bit words {fp32 value, tag}, the
-    // tag being the strip's epoch + 1 (the epoch word lives in the scratch header and is advanced by
-    // the strip's reducer, so every launch - also a replay of a captured graph - uses fresh tags).
+    // tag being the launch epoch + 1 (the epoch word lives in the scratch header and is advanced once
+    // per launch, see read_epoch_and_count, so every launch - also a replay of a captured graph - uses
+    // fresh tags and stale slots of earlier launches never match).
     // The reducer of a strip is its LAST contributor in CTA order, i.e. the CTA whose slice reaches
     // the end of the strip; that slice is the first one of the CTA, and the reduction is postponed to
     // the CTA's end (finish_cta), when the other contributors have normally finished.  It then
@@ -411,106 +415,7 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
       }
     };
 
-    if constexpr (!C::kAlt) {
-      // ---------------------------------------------------------------- both teams on every segment
-      // Team t expands unit t of the segment and reads back rows [t NT/2, (t+1) NT/2) of its
-      // accumulator tile R - 1 segments later.
-      constexpr int DEFER = R - 1;
-      const uint32_t d_base = lane_base + C::kTmemD + team * HN;     // + r * NT
-      const uint32_t a_base = lane_base + C::kTmemA + team * 32;     // + r * 64
-      float acc[HN];
-#pragma unroll
-      for (int m = 0; m < HN; ++m) acc[m] = 0.f;
-      int stage = 0, r = 0, rb = 0;                  // weights stage, ring entry to fill, ring entry to read back
-      uint32_t wphase = 0, rbphase = 0;
-      int strip_lin = strip_first;
-      int u = U0;
-      while (u < U1) {
-        const Slice sl = open_slice(strip_lin, u);
-        const bool is6 = sl.is6;
-        const bool col_live = c < sl.nq * kQuadCols;     // padded quads of a ragged strip hold no data
-        const uint32_t unit_bytes = sl.nq * (is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
-        int unit = u - sl.s_begin;
-        const int unit1 = sl.u1 - sl.s_begin;
-        const uint32_t my_off = team * unit_bytes + lds_lo;
-        const uint32_t two_off = team * unit_bytes + sl.nq * kInt4UnitQuadBytes + c * 16;
-        const int scale_stride = sl.nq * kQuadCols;
-        const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.S) +
-                                   (sl.group ? int4_scale_offset(geo, sl.strip, 0) + c + (size_t)(unit >> 1) * scale_stride : 0);
-        int npend = 0;                                   // segments whose accumulator tile is not read back yet
-        float pend[DEFER];                               // their group scales, oldest first
-#pragma unroll
-        for (int i = 0; i < DEFER; ++i) pend[i] = 1.f;
-
-        auto read_back_oldest = [&]() {
-          mbar_wait_bounded(done + 8 * rb, rbphase, p.status, dead);
-          tc_fence_after();
-          const float scale = pend[0];
-          const uint32_t d_tmem = d_base + rb * NT;
-          if (HN == 8) {
-            float d[8];
-            tc_ld8(d_tmem, d);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = fmaf(scale, d[i], acc[i]);
-          } else {
-#pragma unroll
-            for (int m0 = 0; m0 < HN; m0 += 16) {
-              float d[16];
-              tc_ld16(d_tmem + m0, d);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) acc[(m0 + i) % HN] = fmaf(scale, d[i], acc[(m0 + i) % HN]);
-            }
-          }
-#pragma unroll
-          for (int i = 0; i + 1 < DEFER; ++i) pend[i] = pend[i + 1];
-          if (++rb == R) { rb = 0; rbphase ^= 1; }
-          --npend;
-        };
-
-        while (unit < unit1) {
-          const int cnt = ((unit & 1) == 0 && unit + 1 < unit1) ? 2 : 1;
-          // 1.0 unless the strip has group scales; converted only when queued, so the load's latency is hidden
-          unsigned short scale_raw = 0x3C00;
-          if (sl.group && col_live) scale_raw = __ldg(sp);
-          sp += scale_stride;
-          mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
-          if (team < cnt) {                              // this team's unit exists in the segment
-            // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
-            const uint8_t* st = smem + stage * kStageW;
-            const uint4 lo = *reinterpret_cast<const uint4*>(st + my_off);          // words 0..3
-            const uint4 hi = *reinterpret_cast<const uint4*>(st + (my_off ^ 16));   // words 4..7
-            uint4 two = make_uint4(0, 0, 0, 0);
-            if (is6) two = *reinterpret_cast<const uint4*>(st + two_off);
-            // The operand slot and the accumulator tile of ring entry r were last used R segments ago;
-            // that segment was read back (after a wait on its `done`) before this point in program order.
-            expand_unit(is6, lo, hi, two, a_base + r * 64);
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
-          tc_wait_st();
-          tc_fence_before();
-          if (lane == 0) mbar_arrive(ready + 8 * r);
-          if (npend == DEFER) read_back_oldest();       // segment n - DEFER: its MMAs finished long ago
-          {
-            const float sc = __half2float(__ushort_as_half(scale_raw));
-#pragma unroll
-            for (int i = 0; i < DEFER; ++i)
-              if (npend == i) pend[i] = sc;
-          }
-          ++npend;
-          unit += cnt;
-          if (++stage == S) { stage = 0; wphase ^= 1; }
-          if (++r == R) r = 0;
-        }
-        while (npend > 0) read_back_oldest();
-        u = sl.u1;
-        finish_slice(sl, acc);
-#pragma unroll
-        for (int m = 0; m < HN; ++m) acc[m] = 0.f;
-        ++strip_lin;
-      }
-      finish_cta();
-    } else {
+    {
       // ---------------------------------------------------------------- the teams take alternate segments
       // Team t owns the segments with global index n = t, t + 2, ...: it expands both units, and after
       // storing segment n it reads back all NT rows of segment n - 2.  Two independent chains per CTA
@@ -640,8 +545,6 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
 }
 
 using Tc5Rows16 = Tc5Cfg<16, 12, 6, 1, 4>;
-using Tc5Rows32 = Tc5Cfg<32, 7, 2, 2, 0>;
-using Tc5Rows64 = Tc5Cfg<64, 6, 2, 2, 0>;
 
 bool g_overlap_launches = false;
 
@@ -670,24 +573,19 @@ cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-int tc5_rows_per_pass() { return 64; }
-
 void tc5_set_overlap(bool on) { g_overlap_launches = on; }
 bool tc5_get_overlap() { return g_overlap_launches; }
 
 // CTAs per SM the kernel is sized for, for `rows` rows of A in one pass.
-int tc5_ctas_per_sm(int rows) { return rows <= 16 ? Tc5Rows16::kCtasPerSm : (rows <= 32 ? Tc5Rows32::kCtasPerSm : Tc5Rows64::kCtasPerSm); }
+int tc5_ctas_per_sm(int rows) { (void)rows; return Tc5Rows16::kCtasPerSm; }
 
 size_t tc5_scratch_bytes(int ctas, int rows) {
-  const int nt = rows <= 16 ? 16 : (rows <= 32 ? 32 : 64);
+  (void)rows;
+  const int nt = 16;
   return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * nt * kStripCols * sizeof(unsigned long long);
 }
 
-// Runs the GEMM for rows [0, p.M) with p.M <= 64; the host dispatcher loops over larger M.
-cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream) {
-  if (p.M <= 16) return launch_tc5<Tc5Rows16>(p, stream);
-  if (p.M <= 32) return launch_tc5<Tc5Rows32>(p, stream);
-  return launch_tc5<Tc5Rows64>(p, stream);
-}
+// Runs the GEMM for rows [0, p.M) with p.M <= 16.
+cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream) { return launch_tc5<Tc5Rows16>(p, stream); }
 
 }  // namespace fp6m

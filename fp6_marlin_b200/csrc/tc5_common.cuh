@@ -114,11 +114,6 @@ __device__ __forceinline__ uint32_t atomic_add_relaxed_u32(unsigned int* addr, u
   asm volatile("atom.relaxed.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
   return old;
 }
-__device__ __forceinline__ int atomic_add_acq_rel(int* addr, int v) {
-  int old;
-  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
-  return old;
-}
 
 // Launch epoch.  Every CTA of a launch reads the epoch word and then counts itself; the CTA that
 // completes the count knows that all have read it and advances it for the next launch (also for
