@@ -62,8 +62,9 @@ def measured_peaks():
     if os.path.isfile(path):
         with open(path) as f:
             d = json.load(f)
-        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -367,7 +368,7 @@ def b200_arm(args):
 
 def read_traffic_from_profile():
     """DRAM bytes per launch of the GEMM kernel from the committed ncu summary, if one exists."""
-    path = os.path.join(ROOT, "profiles", "w46_gemm_mma_traffic.json")
+    path = os.path.join(ROOT, "profiles", "w46_gemm_tc5_traffic.json")
     if os.path.isfile(path):
         with open(path) as f:
             return json.load(f).get("dram_bytes_per_launch_full_size")
@@ -378,15 +379,16 @@ def run_sweep(fm, synth, dev, peaks):
     """Latency / GB/s / TFLOP/s of other shapes (graph-timed like `value`); extra information."""
     import torch
     out = []
-    shapes = [("cfg1", K_DIM, N_DIM, m) for m in (1, 2, 4, 8, 16, 32, 64)]
+    shapes = [("cfg1", K_DIM, N_DIM, m) for m in (1, 2, 4, 8, 16, 32, 64, 128)]
     for name, (k, n) in synth.LLAMA2_7B.items():
-        shapes += [(f"7b_{name}", k, n, m) for m in (1, 16)]
+        shapes += [(f"7b_{name}", k, n, m) for m in (1, 16, 128)]
+    shapes += [("cfg4", 16384, 16384, m) for m in (1024, 4096)]      # tensor-bound: compare with the bf16 GEMM peak
     cache = {}
     for tag, k, n, m in shapes:
         if (k, n) not in cache:
             cache.clear()
             wt = synth.make_layer(k, n, QUANT_COLS, GROUP, seed=1, keep_dequantized=False, quant_device=dev)
-            ncopies = max(2, int(300e6 // (wt.B.numel() * 4)) + 1)
+            ncopies = max(2, int(300e6 // (wt.B.numel() * 4)) + 1) if m < 1024 else 1   # large M re-streams B per 256 rows anyway
             cache[(k, n)] = [(wt.B.to(dev).clone(), wt.s.to(dev).clone()) for _ in range(ncopies)]
         copies = cache[(k, n)]
         a = synth.make_activations(m, k).to(dev)
@@ -398,7 +400,7 @@ def run_sweep(fm, synth, dev, peaks):
                 fm.mul(a, *copies[i % len(copies)][:1], c, copies[i % len(copies)][1], ws, QUANT_COLS, group_size=GROUP, layout="b200")
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            reps = 200
+            reps = 200 if m <= 128 else 4
             with torch.cuda.graph(g, stream=stream):
                 for i in range(reps):
                     B, s = copies[i % len(copies)]
@@ -415,7 +417,8 @@ def run_sweep(fm, synth, dev, peaks):
         nbytes = synth.algorithmic_bytes(m, k, n, QUANT_COLS, GROUP)
         fl = synth.flops(m, k, n)
         out.append({"shape": tag, "M": m, "K": k, "N": n, "us": us, "GBs": nbytes / us / 1e3, "TFLOPs": fl / us / 1e6,
-                    "hbm_frac": nbytes / us / 1e3 / peaks["hbm_gbs"]})
+                    "hbm_frac": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                    "tensor_frac_sustained": fl / us / 1e6 / peaks["bf16_tflops_sustained"]})
     return out
 
 

@@ -1,5 +1,5 @@
 // Device-side building blocks for sm_100a: mbarrier + bulk-TMA wrappers with BOUNDED waits,
-// the in-register dequantisers, and the warp-level tensor-core instruction.
+// and the in-register dequantisers of the operand dump.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -61,19 +61,6 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 // every address the kernels form is independent of loaded data, so the kernel still terminates
 // (with garbage results and a status the host reads) instead of hanging the GPU.  A dead thread
 // skips all later waits.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 // Bounded wait.  `kSleepNs` > 0 is for roles that run far ahead of their consumers (producers): they
 // sleep between polls, so their polling does not take issue slots from the working warps.
 template <int kSleepNs = 0>
@@ -91,13 +78,7 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // ---- bulk TMA (1-D, global -> shared, completion on an mbarrier; no multicast) -----------------
-__device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-// Same with an L2 evict-first policy for data that is streamed once (the weights).
+// With an L2 evict-first policy for data that is streamed once (the weights).
 __device__ __forceinline__ void tma_load_1d_stream(uint32_t dst_smem, const void* src, uint32_t bytes,
                                                    uint32_t bar, uint64_t policy) {
   asm volatile(
@@ -170,13 +151,5 @@ __device__ __forceinline__ void dequant_fp6_word(uint32_t four, uint32_t two, in
   out[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(x1, 0u, 0x3424u)), scale4096));
 }
 
-// ---- warp-level tensor-core tile: D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col) ------
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 }  // namespace fp6m

@@ -140,10 +140,10 @@ struct Schedule {
   int bound[kMaxCtas + 1];
 };
 
-FP6M_HD int unit_cost(const Geometry& g, int strip_linear) {
-  return strip_linear < g.strips4 ? 2 * strip_quads(g.n4, strip_linear)
-                                  : 3 * strip_quads(g.n6, strip_linear - g.strips4);
-}
+// Cost of one unit for the schedule.  The kernels are bound by per-unit instruction work, which does
+// not depend on how many of the strip's 128 columns exist and is only slightly larger for FP6 than
+// for INT4 (measured: CTAs given FP6 units by their byte count finished in half the time).
+FP6M_HD int unit_cost(const Geometry& g, int strip_linear) { return strip_linear < g.strips4 ? 8 : 9; }
 
 // First unit u in [u0, u1] such that the weight of [u0, u) is >= target (u1 if never).
 FP6M_HD int unit_at_cost(const Geometry& g, int u0, int u1, long long target) {

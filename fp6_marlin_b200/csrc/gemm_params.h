@@ -2,6 +2,7 @@
 // kernel parameter space (no host-to-device copy, safe under stream capture).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -34,6 +35,7 @@ bool tc5_get_overlap();
 cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 
 // gemm_wide.cu
+cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUtensorMap* map);
 constexpr int kMaxWideCtas = 192;   // one CTA per SM
 int wide_rows_per_pass();
 int wide_tile_rows(int rows);

@@ -10,8 +10,8 @@
 //   warp 0, 6, 7  weights producers: one bulk TMA copy (cp.async.bulk, mbarrier completion) per
 //               SEGMENT = the one or two 64-row units of a 128-row block that belong to the CTA;
 //               a single lane needs ~500 cycles per copy, so the segments are dealt round robin.
-//   warp 1      activations producer: cp.async copies that lay the segment's activations out as
-//               canonical K-major 8x16-byte core matrices (the B operand of the MMA).
+//   warp 1      activations producer: one tiled TMA copy per unit (16 rows x 64 halves, 128-byte
+//               swizzle = the K-major swizzled B operand of the MMA; rows beyond M read as zero).
 //   warps 2-5   MMA issuers, one per dequantiser team: one lane issues tcgen05.mma (kind::f16, fp32
 //               accumulators in TMEM) for its team's segments and commits completion to mbarriers.
 //               A thread sustains one small MMA per 75-120 cycles, the tensor core one per 32.
@@ -28,7 +28,7 @@
 //               segment a team reads the previous one's tile back (tcgen05.ld), multiplies by the
 //               column's group scale in fp32 and adds to registers.  At the end of a slice (the CTA's
 //               units of one strip) the teams pool their sums through shared memory.
-// Work comes from the byte-weighted stripe schedule (fp6m_layout.h).  Strips shared by several CTAs
+// Work comes from the cost-weighted stripe schedule (fp6m_layout.h).  Strips shared by several CTAs
 // are reduced without atomics or fences on the data path: partials are stored as {value, tag} 64-bit
 // words, the tag being a per-launch epoch, and the strip's last contributor (in CTA order) sums the
 // slots at its end - it only ever waits, with a bound, for lower-numbered CTAs.
@@ -70,7 +70,7 @@ struct Tc5Cfg {
   static constexpr int kNumBars = 2 * kStages + 4 * kRing + 1;
   static_assert(kStages >= kTeams && kRing >= kTeams, "every team needs a stage and a ring entry of its own");
   static constexpr int kXchBytes = kTeams * NT * 128 * 4;   // the teams pool their partial sums at the end of a slice
-  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kXchBytes + kNumBars * 8 + 64;
+  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kXchBytes + kNumBars * 8 + 64 + 1024;   // + alignment slack
   static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
@@ -79,10 +79,12 @@ struct Tc5Cfg {
 };
 
 template <class C>
-__global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(const __grid_constant__ MulParams p) {
+__global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kernel(const __grid_constant__ MulParams p, const __grid_constant__ CUtensorMap amap) {
   constexpr int NT = C::NT, S = C::kStages, R = C::kRing;
   constexpr int kDequantThreads = C::kDequantThreads;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // the swizzled activation stages must start on 1024-byte boundaries
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* act_base = smem + S * kStageW;
   float* xch = reinterpret_cast<float*>(smem + S * kStageW + R * C::kActBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kStageW + R * C::kActBytes + C::kXchBytes);
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
       mbar_init(w_empty + 8 * s, 4);     // the team that read the stage has its words in registers
     }
     for (int r = 0; r < R; ++r) {
-      mbar_init(act_full + 8 * r, 32);   // cp.async completions of the 32 lanes of the activation producer
+      mbar_init(act_full + 8 * r, 1);    // the expect_tx arrival of the activations producer
       mbar_init(ready + 8 * r, 4);       // the segment's team stored the operands into TMEM
       mbar_init(d_free + 8 * r, 4);          // the team that owns the segment has read the accumulator tile back
       mbar_init(done + 8 * r, 1);        // tcgen05.commit: every MMA of the segment has finished
@@ -182,37 +184,23 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
     }
   } else if (warp == 1) {
     // ================================================================== activations producer
-    // lane copies chunks idx = lane + 32 j of a unit: row m = idx / 8, 16-byte chunk kc = idx % 8,
-    // into canonical K-major core-matrix order; everything but the K offset is loop-invariant
-    const int kc = lane & 7, m0 = lane >> 3;          // rows m = m0 + 4 j
-    const half* a_src0 = p.A + (size_t)m0 * p.K + 8 * kc;
-    const uint32_t a_dst0 = smem_u32(act_base) + (kc >> 1) * (NT / 8) * 256 + (kc & 1) * 128 + m0 * 16;
-    const size_t row4 = (size_t)4 * p.K;
-    Walk it;
-    it.init(U0, U1, ups);
-    int r = 0;
-    uint32_t rphase = 0;
-    grid_dependency_wait();                           // A may come from the previous kernel
-    while (it.valid()) {
-      const int cnt = it.count();
-      mbar_wait_bounded<200>(done + 8 * r, rphase ^ 1, p.status, dead);     // the MMAs that read this tile are done
-      const uint32_t dst = a_dst0 + r * C::kActBytes;
-      for (int h = 0; h < cnt; ++h) {
-        const int k0 = (it.unit + h) * kUnitRows;
-        const bool k_ok = k0 + 8 * kc < p.K;
-        const half* src = a_src0 + k0;
-#pragma unroll
-        for (int j = 0; j < NT / 4; ++j) {
-          const bool ok = k_ok && m0 + 4 * j < p.M;
-          // row m: 8-row group m / 8 = j / 2 (256 bytes apart), row in group m % 8 = m0 + 4 (j % 2)
-          cp_async16(dst + h * C::kActUnitBytes + (j >> 1) * 256 + (j & 1) * 64, ok ? (const void*)(src + j * row4) : (const void*)p.A, ok);
-        }
+    if (lane == 0) {
+      Walk it;
+      it.init(U0, U1, ups);
+      int r = 0;
+      uint32_t rphase = 0;
+      grid_dependency_wait();                           // A may come from the previous kernel
+      while (it.valid()) {
+        const int cnt = it.count();
+        mbar_wait_bounded<200>(done + 8 * r, rphase ^ 1, p.status, dead);     // the MMAs that read this tile are done
+        mbar_arrive_expect_tx(act_full + 8 * r, cnt * C::kActUnitBytes);
+        const uint32_t dst = smem_u32(act_base) + r * C::kActBytes;
+        for (int h = 0; h < cnt; ++h)
+          tma_load_act(dst + h * C::kActUnitBytes, &amap, (it.unit + h) * kUnitRows, act_full + 8 * r);
+        if (++r == R) { r = 0; rphase ^= 1; }
+        it.next(cnt);
       }
-      cp_async_arrive(act_full + 8 * r);
-      if (++r == R) { r = 0; rphase ^= 1; }
-      it.next(cnt);
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp >= 2 && warp < 2 + C::kIssuers) {
     // ================================================================== MMA issuer(s)
     // The whole warp walks the segments and waits (warp-uniform control flow and operands); one
@@ -226,13 +214,12 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
       it.init(U0, U1, ups);
       int r = 0, n = 0;
       uint32_t rphase = 0;
-      const uint64_t desc0 = act_desc(smem_u32(act_base));
-      constexpr uint32_t kStepDesc = ((NT / 8) * 256) >> 4;
+      const uint64_t desc0 = wide_act_desc(smem_u32(act_base));
+      constexpr uint32_t kStepDesc = 32 >> 4;            // 16 halves along a 128-byte row
       while (it.valid()) {
         const int cnt = it.count();
         if (kIssuers == 1 || n == mine) {
           mbar_wait_bounded<40>(act_full + 8 * r, rphase, p.status, dead);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote the activations
           mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
           mbar_wait_bounded(d_free + 8 * r, rphase ^ 1, p.status, dead);   // previous tile of this entry was read
           tc_fence_after();
@@ -242,7 +229,7 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
           const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
           if (lane == 0) {
             tc_mma_unit<kStepDesc>(d_tmem, a_tmem, desc, C::kIdesc, 0u);
-            if (cnt == 2) tc_mma_unit<kStepDesc>(d_tmem, a_tmem + 32, desc + 4 * kStepDesc, C::kIdesc, 1u);
+            if (cnt == 2) tc_mma_unit<kStepDesc>(d_tmem, a_tmem + 32, desc + (C::kActUnitBytes >> 4), C::kIdesc, 1u);
             tc_commit(done + 8 * r);
           }
           __syncwarp();
@@ -568,7 +555,10 @@ cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_overlap_launches ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, w46_gemm_tc5_kernel<C>, p);
+  alignas(64) CUtensorMap amap;
+  cudaError_t me = encode_activation_map(p.A, p.M, p.K, C::NT, &amap);
+  if (me != cudaSuccess) return me;
+  return cudaLaunchKernelEx(&cfg, w46_gemm_tc5_kernel<C>, p, amap);
 }
 
 }  // namespace

@@ -53,16 +53,6 @@ struct WideCfg {
   static_assert(kTmemUsed <= 512 && kRowsPerTeam % 16 == 0 && kStages >= kTeams && kRing >= kTeams, "configuration");
 };
 
-// activations of one unit: K-major, 128-byte swizzle (layout type 2), 1024 bytes between 8-row groups;
-// the leading-dimension field is not used by swizzled K-major layouts
-__device__ __forceinline__ uint64_t wide_act_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
-__device__ __forceinline__ void tma_load_act(uint32_t dst, const CUtensorMap* map, int k0, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(k0), "r"(0), "r"(bar) : "memory");
-}
 // INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
 __device__ __forceinline__ void expand_int4_scaled(uint32_t q, half2 s, uint32_t* b) {
   uint32_t e[4];
@@ -439,38 +429,11 @@ using Wide64 = WideCfg<64, 4, 8, 8, 4>;
 using Wide128 = WideCfg<128, 2, 6, 6, 3>;
 using Wide256 = WideCfg<256, 2, 4, 4, 3>;
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The driver's tensor-map encoder, looked up once through the runtime (no link against libcuda).
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
 template <class C>
 cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
-  // A as a K x M tensor (K contiguous): one box = 64 halves x NT rows = the activations of one 64-row unit
-  EncodeTiledFn encode = encode_tiled();
-  if (!encode) return cudaErrorNotSupported;
   alignas(64) CUtensorMap amap;
-  const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
-  const cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)C::NT};
-  const cuuint32_t elem[2] = {1, 1};
-  if (encode(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(p.A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return cudaErrorInvalidValue;
+  cudaError_t me = encode_activation_map(p.A, p.M, p.K, C::NT, &amap);
+  if (me != cudaSuccess) return me;
 
   static bool configured[64] = {};
   int dev = 0;
@@ -494,6 +457,40 @@ cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
 }
 
 }  // namespace
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up once through the runtime (no link against libcuda).
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// A as a K x M tensor (K contiguous): one box = 64 halves x `box_rows` rows = the activations of one
+// 64-row unit, written to shared memory with the 128-byte swizzle; rows beyond M read as zero.
+cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUtensorMap* map) {
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
 
 int wide_rows_per_pass() { return 256; }
 

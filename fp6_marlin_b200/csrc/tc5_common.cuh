@@ -3,6 +3,7 @@
 // epoch, the in-register expanders and the walk over a CTA's units.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
 
@@ -55,11 +56,6 @@ __device__ __forceinline__ void tc_mma_unit(uint32_t d_tmem, uint32_t a_tmem, ui
         "n"(kStepDesc), "n"(2 * kStepDesc), "n"(3 * kStepDesc)
       : "memory");
 }
-// K-major, no swizzle: 8-row x 16-byte core matrices of 128 bytes; the two K halves of a step are
-// 128 bytes apart (leading offset), 8-row groups 256 bytes apart (stride offset).
-__device__ __forceinline__ uint64_t act_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(256 >> 4) << 32) | ((uint64_t)1 << 46);
-}
 __device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
@@ -75,23 +71,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
   tc_wait_ld();
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
-  uint32_t r[8];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr) : "memory");
-  tc_wait_ld();
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-// 16-byte asynchronous copy with zero fill when `valid` is false; completion is reported to an
-// mbarrier by cp_async_arrive below.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const unsigned int* p) {
   uint32_t v;
@@ -115,6 +94,17 @@ __device__ __forceinline__ uint32_t atomic_add_relaxed_u32(unsigned int* addr, u
   return old;
 }
 
+// ---- activations by tiled TMA --------------------------------------------------------------------
+// activations of one unit: K-major, 128-byte swizzle (layout type 2), 1024 bytes between 8-row groups;
+// the leading-dimension field is not used by swizzled K-major layouts
+__device__ __forceinline__ uint64_t wide_act_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
+__device__ __forceinline__ void tma_load_act(uint32_t dst, const CUtensorMap* map, int k0, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(k0), "r"(0), "r"(bar) : "memory");
+}
 // Launch epoch.  Every CTA of a launch reads the epoch word and then counts itself; the CTA that
 // completes the count knows that all have read it and advances it for the next launch (also for
 // the next replay of a captured graph).  The counting atomic takes its address through the loaded

@@ -213,7 +213,7 @@ def test_repack_from_reference_golden(golden_dir, name):
                                          (16384, 16384, 512, 296)])
 def test_schedule_covers_every_unit_once(k, n, qc, ctas):
     """Units are 64 rows of one 128-column strip; every unit belongs to exactly one CTA and the
-    byte weight per CTA is balanced to within one unit."""
+    cost per CTA (8 per INT4 unit, 9 per FP6 unit) is balanced to within one unit."""
     bounds, total = fm.schedule(k, n, qc, 128 if k % 128 == 0 else -1, ctas)
     nq = max(qc, 0)
     s4 = -(-(n - nq) // 128)
@@ -224,14 +224,9 @@ def test_schedule_covers_every_unit_once(k, n, qc, ctas):
     assert all(b1 >= b0 for b0, b1 in zip(bounds, bounds[1:]))
 
     def cost(unit):
-        strip = unit // ups
-        if strip < s4:
-            cols = min(128, (n - nq) - strip * 128)
-            return 2 * -(-cols // 32)
-        cols = min(128, nq - (strip - s4) * 128)
-        return 3 * -(-cols // 32)
+        return 8 if unit // ups < s4 else 9
     costs = np.array([cost(u) for u in range(total)], dtype=np.int64)
     csum = np.concatenate([[0], np.cumsum(costs)])
     per_cta = np.array([csum[b1] - csum[b0] for b0, b1 in zip(bounds, bounds[1:])])
     assert per_cta.sum() == costs.sum()
-    assert per_cta.max() <= costs.sum() / ctas + 12 + 1e-9
+    assert per_cta.max() <= costs.sum() / ctas + 9 + 1e-9
