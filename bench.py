@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sweep", action="store_true", help="also time the other M values and layer shapes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-shape", default=None, metavar="K,N,M",
+                    help="time just this shape the way --sweep does and print its record (used for profiling other shapes)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch the GEMMs without programmatic dependent launch (no overlap of consecutive steps)")
     return ap.parse_args()
@@ -231,6 +233,11 @@ def b200_arm(args):
     assert torch.cuda.is_available(), "bench.py needs a CUDA GPU (no CPU fallback)"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.only_shape:
+        k, n, m = (int(x) for x in args.only_shape.split(","))
+        fm.set_launch_overlap(not args.no_overlap)
+        print(json.dumps(run_sweep(fm, synth, dev, measured_peaks(), only=(k, n, m))[0]))
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node == --gpus"
@@ -375,7 +382,7 @@ def read_traffic_from_profile():
     return None
 
 
-def run_sweep(fm, synth, dev, peaks):
+def run_sweep(fm, synth, dev, peaks, only=None):
     """Latency / GB/s / TFLOP/s of other shapes (graph-timed like `value`); extra information."""
     import torch
     out = []
@@ -383,6 +390,8 @@ def run_sweep(fm, synth, dev, peaks):
     for name, (k, n) in synth.LLAMA2_7B.items():
         shapes += [(f"7b_{name}", k, n, m) for m in (1, 16, 128)]
     shapes += [("cfg4", 16384, 16384, m) for m in (1024, 4096)]      # tensor-bound: compare with the bf16 GEMM peak
+    if only is not None:
+        shapes = [("only",) + tuple(only)]
     cache = {}
     for tag, k, n, m in shapes:
         if (k, n) not in cache:
