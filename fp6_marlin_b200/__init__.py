@@ -7,12 +7,13 @@ this package fails if that library has not been built - there is no fallback pat
 """
 from .api import (b200_sizes, dequantize, device_status, dump_operands, mul, pack_b200, prepacking,
                   quantize, repack_from_reference, schedule, set_launch_overlap, unpack_b200)
+from .linear import W46Linear
 from .quant import (W46Weight, decode_fp6, encode_fp6, fake_quantize_fp6, make_w46_weight,
                     quantize_fp6, quantize_int4, select_outlier_columns)
 
 __all__ = [
     "prepacking", "quantize", "dequantize", "mul",
     "b200_sizes", "pack_b200", "unpack_b200", "repack_from_reference", "schedule", "dump_operands",
-    "device_status", "set_launch_overlap", "W46Weight", "make_w46_weight", "quantize_int4", "quantize_fp6", "encode_fp6",
+    "device_status", "set_launch_overlap", "W46Linear", "W46Weight", "make_w46_weight", "quantize_int4", "quantize_fp6", "encode_fp6",
     "decode_fp6", "fake_quantize_fp6", "select_outlier_columns",
 ]

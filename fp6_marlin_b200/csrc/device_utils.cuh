@@ -77,7 +77,7 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity,
   if (status) atomicExch(status, kStatusTimeout);
 }
 
-// ---- bulk TMA (1-D, global -> shared, completion on an mbarrier; no multicast) -----------------
+// ---- bulk TMA (1-D, global -> shared of this CTA, completion on an mbarrier) -------------------
 // With an L2 evict-first policy for data that is streamed once (the weights).
 __device__ __forceinline__ void tma_load_1d_stream(uint32_t dst_smem, const void* src, uint32_t bytes,
                                                    uint32_t bar, uint64_t policy) {

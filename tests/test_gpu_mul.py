@@ -270,3 +270,25 @@ def test_wide_long_k_and_split_strips():
     assert err <= TOL, err
     err, _ = _run(40, 8192, 512, -1, 128, 64, 256, seed=4)
     assert err <= TOL, err
+
+
+@pytest.mark.gpu
+def test_w46_linear_forward_matches_dequantised_matmul():
+    dev = _dev()
+    torch.manual_seed(1)
+    out_f, in_f, qc = 768, 512, 256
+    w = torch.randn(out_f, in_f) * 0.02
+    w[torch.randperm(out_f)[:qc]] *= 8
+    bias = torch.randn(out_f).half()
+    x = torch.randn(3, 5, in_f).half()
+    for restore in (True, False):
+        layer = fm.W46Linear(w.half(), quant_cols=qc, group_size=128, bias=bias, restore_order=restore).to(dev)
+        y = layer(x.to(dev)).float().cpu()
+        perm = layer.output_permutation.cpu()
+        w_kn = w.half().t().contiguous()[:, perm]
+        ref = F.gemm_reference(x.reshape(-1, in_f).numpy(), _oracle_weight(w_kn, qc, 128))       # columns in mul's order
+        ref = torch.from_numpy(ref) + bias.float()[perm]
+        if restore:
+            ref = ref[:, layer.inverse_permutation.cpu()]
+        err = (torch.linalg.norm(y.reshape(-1, out_f) - ref) / torch.linalg.norm(ref)).item()
+        assert err <= 2 * TOL, (restore, err)        # the bias is added in fp16 after the GEMM's own rounding

@@ -230,3 +230,21 @@ def test_schedule_covers_every_unit_once(k, n, qc, ctas):
     per_cta = np.array([csum[b1] - csum[b0] for b0, b1 in zip(bounds, bounds[1:])])
     assert per_cta.sum() == costs.sum()
     assert per_cta.max() <= costs.sum() / ctas + 9 + 1e-9
+
+
+def test_w46_linear_bookkeeping():
+    """The linear wrapper moves the largest-magnitude output features to the FP6 end and remembers how."""
+    torch.manual_seed(0)
+    out_f, in_f, qc = 512, 256, 256
+    w = torch.randn(out_f, in_f) * 0.02
+    hot = torch.randperm(out_f)[:qc]
+    w[hot] *= 8
+    layer = fm.W46Linear(w.half(), quant_cols=qc, group_size=128)
+    perm, inv = layer.output_permutation, layer.inverse_permutation
+    assert sorted(perm.tolist()) == list(range(out_f))
+    assert torch.equal(perm[inv], torch.arange(out_f)) and torch.equal(inv[perm], torch.arange(out_f))
+    assert set(perm[out_f - qc:].tolist()) == set(hot.tolist())            # the outliers are the FP6 columns
+    assert perm[: out_f - qc].tolist() == sorted(perm[: out_f - qc].tolist())   # the others keep their order
+    nwords, nscales = fm.b200_sizes(in_f, out_f, qc, 128)
+    assert layer.B.numel() == nwords and layer.s.numel() == nscales
+    assert "fp6_columns=256" in repr(layer)
