@@ -36,6 +36,8 @@ SIGNATURES = {
     "fp6m_mul_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _i, _vp,
                                      _i, _i, _i, _i, _i, _i, _i, _vp]),
     "fp6m_dump_operands": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "fp6m_encode_fp6_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]),
+    "fp6m_pack_b200_device": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2 + [ctypes.c_int, ctypes.c_void_p]),
     "fp6m_set_launch_overlap": (ctypes.c_int, [ctypes.c_int]),
     "fp6m_last_cuda_error": (ctypes.c_char_p, []),
     "fp6m_version": (ctypes.c_char_p, []),

@@ -134,6 +134,62 @@ def pack_b200(q4, c6, s4, s6, k: int, n: int, quant_cols: int = -1, group_size: 
     return B, s
 
 
+def pack_b200_gpu(q4, c6, s4, s6, k: int, n: int, quant_cols: int = -1, group_size: int = -1):
+    """:func:`pack_b200` on the GPU: CUDA tensors in, (B, s) on the same device out, same bytes.
+    Asynchronous on the current stream; padding bytes of the buffers are zero."""
+    qc = max(quant_cols, 0)
+    device = next(t.device for t in (q4, c6, s4, s6) if t is not None)
+    if device.type != "cuda":
+        raise ValueError("pack_b200_gpu: the inputs must be CUDA tensors")
+    words, nscales = b200_sizes(k, n, quant_cols, group_size)
+    B = torch.zeros(words, dtype=torch.int32, device=device)
+    s = torch.zeros(nscales, dtype=torch.float16, device=device)
+
+    def prep(t, dtype, numel):
+        if numel == 0:
+            return None, 0
+        if t is None:
+            raise ValueError("pack_b200_gpu: a region with columns needs its codes and scales")
+        t = t.detach().to(device).contiguous()
+        if t.dtype != dtype or t.numel() != numel:
+            raise ValueError(f"pack_b200_gpu: expected {numel} elements of {dtype}, got {t.numel()} of {t.dtype}")
+        return t, _ptr(t)
+
+    groups = (k + 127) // 128 if group_size > 0 else 1
+    q4_t, q4_p = prep(q4, torch.uint8, k * (n - qc))
+    c6_t, c6_p = prep(c6, torch.uint8, k * qc)
+    s4_t, s4_p = prep(s4, torch.float16, groups * (n - qc))
+    s6_t, s6_p = prep(s6, torch.float16, qc)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = lib.fp6m_pack_b200_device(q4_p, c6_p, s4_p, s6_p, k, n, quant_cols, group_size, _ptr(B), _ptr(s),
+                                       device.index if device.index is not None else torch.cuda.current_device(), stream)
+    if rc:
+        raise RuntimeError(f"fp6m_pack_b200_device failed with code {rc}: {_lib.last_cuda_error()}")
+    return B, s
+
+
+def encode_fp6_gpu(x: torch.Tensor) -> torch.Tensor:
+    """fp16 CUDA tensor of values in the FP6 range -> codes ``s eee mm`` (uint8) on the same device, the
+    truncating cast of the reference (weight_quant.cpp:27-91).  Raises ``ValueError`` for out-of-range
+    input like the host function (this check synchronises)."""
+    if x.dtype != torch.float16:
+        raise ValueError("Input tensor should be of type float16.")
+    if x.device.type != "cuda":
+        raise ValueError("encode_fp6_gpu: the input must be a CUDA tensor")
+    src = x.detach().contiguous()
+    codes = torch.empty(src.shape, dtype=torch.uint8, device=src.device)
+    flag = torch.zeros(1, dtype=torch.int32, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = lib.fp6m_encode_fp6_device(_ptr(src), _ptr(codes), src.numel(), src.device.index,
+                                        torch.cuda.current_stream(src.device).cuda_stream, _ptr(flag))
+    if rc:
+        raise RuntimeError(f"fp6m_encode_fp6_device failed with code {rc}")
+    if int(flag.item()) == _lib.ERR_VALUE_RANGE:
+        raise ValueError("Input value out of range for FP6.")
+    return codes
+
+
 def unpack_b200(B: torch.Tensor, s: torch.Tensor, k: int, n: int, quant_cols: int = -1, group_size: int = -1):
     """Inverse of :func:`pack_b200`: returns (q4, c6, s4, s6) as CPU tensors."""
     qc = max(quant_cols, 0)

@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from ._lib import lib
-from .api import pack_b200
+from .api import encode_fp6_gpu, pack_b200, pack_b200_gpu
 
 FP6_MAX = 28.0
 FP6_MIN = 0.0625
@@ -87,7 +87,7 @@ def quantize_fp6(w: torch.Tensor):
     """fp16 W[k, n] -> (codes uint8 [k, n], scales fp16 (n,), W_deq fp16 [k, n]); W_deq is the exact
     code value times the column scale with one fp16 multiply, as ``dequantize`` returns it."""
     x, s = fake_quantize_fp6(w)
-    codes = encode_fp6(x)
+    codes = encode_fp6_gpu(x) if x.device.type == "cuda" else encode_fp6(x)
     deq = decode_fp6(codes) * s.reshape(1, -1)
     return codes, s, deq
 
@@ -112,20 +112,25 @@ def make_w46_weight(w: torch.Tensor, quant_cols: int = -1, group_size: int = 128
                     quant_device=None) -> W46Weight:
     """Quantise and pack fp16 W[k, n] whose last ``quant_cols`` columns are to be FP6 and the rest
     INT4 - the counterpart of ``gen_mixed_weight`` (test.py:123-152) for the b200 layout.
-    ``quant_device`` lets the elementwise INT4 rule run on a GPU (same IEEE fp16 arithmetic); the
-    result is a CPU-resident weight either way."""
+    With ``quant_device`` (a CUDA device) everything - the INT4 rule, the FP6 scaling and truncating
+    cast, the packing - runs on that GPU (same IEEE fp16 arithmetic, same bytes) and the weight stays
+    there; without it the weight is prepared and kept on the CPU."""
     k, n = w.shape
     qc = max(quant_cols, 0)
     w4, w6 = w[:, : n - qc], w[:, n - qc:]
     q4 = s4 = d4 = c6 = s6 = d6 = None
+    on_gpu = quant_device is not None and torch.device(quant_device).type == "cuda"
     if n - qc > 0:
         src = w4.contiguous() if quant_device is None else w4.to(quant_device).contiguous()
-        q4, s4, d4 = (t.cpu() for t in quantize_int4(src, group_size))
+        q4, s4, d4 = quantize_int4(src, group_size)
         if not keep_dequantized:
             d4 = None
     if qc > 0:
-        c6, s6, d6 = quantize_fp6(w6.contiguous())
-    B, s = pack_b200(q4, c6, s4, s6, k, n, quant_cols, group_size)
+        src = w6.contiguous() if quant_device is None else w6.to(quant_device).contiguous()
+        c6, s6, d6 = quantize_fp6(src)
+        if not keep_dequantized:
+            d6 = None
+    B, s = (pack_b200_gpu if on_gpu else pack_b200)(q4, c6, s4, s6, k, n, quant_cols, group_size)
     deq = None
     if keep_dequantized:
         deq = torch.cat([d for d in (d4, d6) if d is not None], dim=1).contiguous()

@@ -138,6 +138,15 @@ int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, 
                        int group_size, int dev, void* stream);
 
 /* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
+/* Device-side weight preparation.  The reference prepares weights in single-threaded host loops
+ * (fp6_marlin/weight_quant.cpp:106-124, fp6_marlin/weight_prepacking.cpp:123-177); these two do the same
+ * work on the GPU, asynchronously on `stream`, with device pointers, and produce the same bytes as
+ * fp6m_encode_fp6 and fp6m_pack_b200.  An out-of-range FP6 input is coded 0 and FP6M_ERR_VALUE_RANGE is
+ * written to the optional device int `status_dev`.  No counterpart in the reference. */
+int fp6m_encode_fp6_device(const void* w, void* codes, size_t count, int dev, void* stream, int* status_dev);
+int fp6m_pack_b200_device(const void* q4, const void* c6, const void* s4, const void* s6, int K, int N, int quant_cols,
+                          int group_size, void* B_out, void* s_out, int dev, void* stream);
+
 /* Process-wide option, off by default; returns the previous setting (a negative argument only queries).
  * When on, the GEMM kernels are launched with programmatic stream serialisation: a GEMM may begin its
  * set-up and prefetch B while the kernel before it in the stream is still finishing.  Everything else

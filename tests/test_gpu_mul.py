@@ -292,3 +292,32 @@ def test_w46_linear_forward_matches_dequantised_matmul():
             ref = ref[:, layer.inverse_permutation.cpu()]
         err = (torch.linalg.norm(y.reshape(-1, out_f) - ref) / torch.linalg.norm(ref)).item()
         assert err <= 2 * TOL, (restore, err)        # the bias is added in fp16 after the GEMM's own rounding
+
+
+@pytest.mark.gpu
+def test_gpu_weight_preparation_matches_host_bytes():
+    """Quantise + cast + pack on the GPU gives the same packed words and scales as the host path."""
+    dev = _dev()
+    for (k, n, qc, gs) in [(256, 512, 256, 128), (384, 1280 + 32, 32, 128), (192, 320, 64, -1), (256, 256, 256, -1), (512, 384, -1, 128)]:
+        w = synth.make_weight_fp16(k, n, qc, seed=k + n)
+        host = fm.make_w46_weight(w, qc, gs)
+        gpu = fm.make_w46_weight(w, qc, gs, quant_device=dev)
+        assert gpu.B.device.type == "cuda"
+        assert torch.equal(gpu.B.cpu(), host.B), (k, n, qc, gs)
+        assert torch.equal(gpu.s.cpu().view(torch.int16), host.s.view(torch.int16)), (k, n, qc, gs)
+        assert torch.equal(gpu.w_deq.cpu().view(torch.int16), host.w_deq.view(torch.int16)), (k, n, qc, gs)
+
+
+@pytest.mark.gpu
+def test_gpu_fp6_cast_matches_host_on_every_in_range_half():
+    dev = _dev()
+    bits = torch.arange(0, 1 << 16, dtype=torch.int32).to(torch.int16)
+    vals = bits.view(torch.float16)
+    mag = vals.abs().float()
+    ok = (mag == 0) | ((mag >= 0.0625) & (mag <= 28.0))
+    x = vals[ok].contiguous()
+    assert torch.equal(fm.encode_fp6_gpu(x.to(dev)).cpu(), fm.encode_fp6(x))
+    with pytest.raises(ValueError):
+        fm.encode_fp6_gpu(torch.tensor([0.01, 1.0], dtype=torch.float16, device=dev))
+    with pytest.raises(ValueError):
+        fm.encode_fp6_gpu(torch.tensor([29.0], dtype=torch.float16, device=dev))
