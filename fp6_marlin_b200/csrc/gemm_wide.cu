@@ -11,9 +11,13 @@
 //     rows, 128-byte swizzle) - the K-major swizzled operand layout of tcgen05 with 1024 bytes between
 //     8-row groups; a K step of 16 advances the descriptor by 32 bytes.  Rows beyond M are zero-filled
 //     by the copy engine.
-//   * One thread issues all MMAs in segment order, so the summation order is fixed.
-// One CTA per SM: warp 0 weights producer, warp 1 activations producer, warp 2 MMA issuer (and TMEM
-// owner), warp 3 launch epoch, then four dequantiser warps per team; teams take the segments in turn.
+//   * 256-row tiles have one MMA issuer.  Narrower tiles, whose MMAs are shorter than the ~100 cycles
+//     one thread needs to issue one, have 2 or 4 issuers: issuer i takes the segments n = i, i + I, ...
+//     into its own accumulator tile and the tiles are added, in issuer order, when a slice is written
+//     out - the summation order is fixed either way.
+// One CTA per SM: warp 0 weights producer, warp 1 activations producer, warps 2.. MMA issuers (warp 2
+// owns TMEM, the last one reads the launch epoch), then four dequantiser warps per team; teams take the
+// segments in turn.
 // Split-K between CTAs uses the tagged slots of gemm_tc5.cu (the strip's last contributor reduces).
 //
 // Replaces the reference's large-tile path (thread_m_blocks 2..4 and its `parallel` batches,
@@ -31,20 +35,21 @@ namespace fp6m {
 
 namespace {
 
-template <int NT_, int TEAMS_, int STAGES_, int ACT_STAGES_, int RING_>
+template <int NT_, int TEAMS_, int ISSUERS_, int STAGES_, int ACT_STAGES_, int RING_>
 struct WideCfg {
+  static constexpr int kIssuers = ISSUERS_;            // MMA issuers = accumulator tiles
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kTeams = TEAMS_;
   static constexpr int kStages = STAGES_;              // weight stages (one segment = up to two units each)
   static constexpr int kActStages = ACT_STAGES_;       // activation stages (one unit each)
   static constexpr int kRing = RING_;                  // TMEM operand slots (one segment each)
-  static constexpr int kDeqBase = 4;
+  static constexpr int kDeqBase = (2 + kIssuers + 3) & ~3;
   static constexpr int kThreads = 32 * (kDeqBase + 4 * kTeams);
   static constexpr int kDequantThreads = 128 * kTeams;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves, 1024-byte aligned stages
   static constexpr int kNumBars = 2 * kStages + 2 * kActStages + 2 * kRing + 3;
   static constexpr int kSmemBytes = kStages * kStageW + kActStages * kActUnitBytes + kNumBars * 8 + 64 + 1024;
-  static constexpr int kTmemD = 0, kTmemA = NT;        // the accumulator tile, then operand slots of 64 columns
+  static constexpr int kTmemD = 0, kTmemA = kIssuers * NT;   // the accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
   static constexpr int kSlotWords = NT * kStripCols;
@@ -102,7 +107,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       mbar_init(ready + 8 * r, 4);       // the segment's team stored the operands into TMEM
       mbar_init(slot_free + 8 * r, 1);   // tcgen05.commit: the MMAs that read the slot have finished
     }
-    mbar_init(slice_done, 1);            // tcgen05.commit: the accumulator tile holds the whole slice
+    mbar_init(slice_done, C::kIssuers);  // tcgen05.commit of every issuer: the accumulator tiles hold the whole slice
     mbar_init(d_read, 4 * T);            // every dequantiser warp has read its part of the tile back
     mbar_init(epoch_bar, 1);
     mbar_fence_init();
@@ -169,53 +174,65 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         it.next(cnt);
       }
     }
-  } else if (warp == 2) {
-    // ================================================================== MMA issuer
+  } else if (warp >= 2 && warp < 2 + C::kIssuers) {
+    // ================================================================== MMA issuers
     // The whole warp walks the segments and waits; one fixed lane issues, so the commits track its MMAs.
-    Walk it;
-    it.init(U0, U1, ups);
-    int r = 0, sa = 0, slices = 0;
-    uint32_t rphase = 0, aphase = 0;
-    bool first = true;                                // next MMA is the first of a slice: it overwrites the tile
-    constexpr uint32_t kStepDesc = 32 >> 4;            // 16 halves along a 128-byte row
-    const uint64_t desc0 = wide_act_desc(smem_u32(act_base));
-    while (it.valid()) {
-      const int cnt = it.count();
-      mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
-      if (first && slices > 0) mbar_wait_bounded<40>(d_read, (slices - 1) & 1, p.status, dead);   // previous slice was read back
-      const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
-      for (int h = 0; h < cnt; ++h) {
-        mbar_wait_bounded<40>(a_full + 8 * sa, aphase, p.status, dead);
-        tc_fence_after();
-        // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
-        const uint64_t desc = desc0 + (uint64_t)(sa * (C::kActUnitBytes >> 4));
-        if (lane == 0) {
-          tc_mma_unit<kStepDesc>(tmem + C::kTmemD, a_tmem + h * 32, desc, C::kIdesc, first ? 0u : 1u);
-          tc_commit(a_empty + 8 * sa);                  // the stage may be refilled when these MMAs are done
-        }
-        __syncwarp();
-        first = false;
-        if (++sa == RA) { sa = 0; aphase ^= 1; }
-      }
-      const bool slice_ends = it.next(cnt) || !it.valid();
-      if (lane == 0) {
-        tc_commit(slot_free + 8 * r);
-        if (slice_ends) tc_commit(slice_done);
-      }
-      __syncwarp();
-      if (slice_ends) { first = true; ++slices; }
-      if (++r == R) { r = 0; rphase ^= 1; }
-    }
-  } else if (warp == 3) {
-    if (lane == 0) {
+    constexpr int I = C::kIssuers;
+    const int mine = warp - 2;
+    if (mine == I - 1 && lane == 0) {
       // the tag of this launch's split-K partials is epoch + 1
       grid_dependency_wait();
       const uint32_t e = read_epoch_and_count(p.epochs, gridDim.x);
       misc[1] = e;
       mbar_arrive(epoch_bar);
     }
-  } else {
-    // ================================================================== dequantisers (warps 4..)
+    __syncwarp();
+    Walk it;
+    it.init(U0, U1, ups);
+    int r = 0, sa = 0, slices = 0, turn = 0;
+    uint32_t rphase = 0, aphase = 0;
+    bool first = true;                                // my next MMA is my first of the slice: it overwrites my tile
+    constexpr uint32_t kStepDesc = 32 >> 4;            // 16 halves along a 128-byte row
+    const uint64_t desc0 = wide_act_desc(smem_u32(act_base));
+    const uint32_t d_tmem = tmem + C::kTmemD + mine * NT;
+    while (it.valid()) {
+      const int cnt = it.count();
+      const bool my_turn = I == 1 || turn == mine;
+      if (my_turn) {
+        mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
+        if (first && slices > 0) mbar_wait_bounded<40>(d_read, (slices - 1) & 1, p.status, dead);   // previous slice was read back
+      }
+      const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
+      for (int h = 0; h < cnt; ++h) {
+        if (my_turn) {
+          mbar_wait_bounded<40>(a_full + 8 * sa, aphase, p.status, dead);
+          tc_fence_after();
+          // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
+          const uint64_t desc = desc0 + (uint64_t)(sa * (C::kActUnitBytes >> 4));
+          if (lane == 0) {
+            tc_mma_unit<kStepDesc>(d_tmem, a_tmem + h * 32, desc, C::kIdesc, first ? 0u : 1u);
+            tc_commit(a_empty + 8 * sa);                  // the stage may be refilled when these MMAs are done
+          }
+          __syncwarp();
+          first = false;
+        }
+        if (++sa == RA) { sa = 0; aphase ^= 1; }
+      }
+      const bool slice_ends = it.next(cnt) || !it.valid();
+      // An issuer without work in a slice runs ahead; its arrival for slice k must not be counted
+      // towards slice k - 1, so it first sees that phase complete.
+      if (slice_ends && I > 1 && slices > 0) mbar_wait_bounded<40>(slice_done, (slices - 1) & 1, p.status, dead);
+      if (lane == 0) {
+        if (my_turn) tc_commit(slot_free + 8 * r);
+        if (slice_ends) tc_commit(slice_done);          // completes when all my MMAs so far have finished
+      }
+      __syncwarp();
+      if (slice_ends) { first = true; ++slices; }
+      if (++turn == I) turn = 0;
+      if (++r == R) { r = 0; rphase ^= 1; }
+    }
+  } else if (warp >= C::kDeqBase) {
+    // ================================================================== dequantisers (warps kDeqBase..)
     // thread = weight column = TMEM lane; team t expands the segments n = t, t + T, ... of the CTA
     // and writes out rows [t NT/T, (t+1) NT/T) of every slice's accumulator tile
     constexpr int RPT = C::kRowsPerTeam;
@@ -337,6 +354,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         r += T;
         if (r >= R) { r -= R; rphase ^= 1; }
       }
+      const int n0_slice = n0;
       n0 += nseg;
       u = sl.u1;
 
@@ -356,8 +374,21 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       }
 #pragma unroll 1
       for (int m0 = 0; m0 < RPT; m0 += 16) {
+        // add the issuers' tiles in issuer order; issuer i took the slice's segments j with
+        // (n0_slice + j) % I == i - one that had none keeps a stale tile, which is skipped
         float v[16];
-        tc_ld16(d_base + m0, v);
+#pragma unroll
+        for (int q = 0; q < 16; ++q) v[q] = 0.f;
+#pragma unroll
+        for (int i = 0; i < C::kIssuers; ++i) {
+          const int first_j = (i - n0_slice % C::kIssuers + C::kIssuers) % C::kIssuers;
+          if (first_j < nseg) {
+            float t[16];
+            tc_ld16(d_base + i * NT + m0, t);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] += t[q];
+          }
+        }
         if (whole) {
           store_rows(sl, m0, v, col_scale, writes);
         } else {
@@ -424,10 +455,10 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   }
 }
 
-using Wide32 = WideCfg<32, 2, 8, 8, 4>;
-using Wide64 = WideCfg<64, 4, 8, 8, 4>;
-using Wide128 = WideCfg<128, 2, 6, 6, 3>;
-using Wide256 = WideCfg<256, 2, 4, 4, 3>;
+using Wide32 = WideCfg<32, 2, 4, 8, 8, 6>;      // 4 x 32 + 6 x 64 = 512 TMEM columns
+using Wide64 = WideCfg<64, 4, 4, 8, 8, 4>;      // 4 x 64 + 4 x 64
+using Wide128 = WideCfg<128, 2, 2, 6, 6, 4>;    // 2 x 128 + 4 x 64
+using Wide256 = WideCfg<256, 2, 1, 4, 4, 3>;    // 256 + 3 x 64
 
 template <class C>
 cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
