@@ -86,11 +86,19 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   DeviceGuard guard(dev);
   if (sms <= 0) sms = sm_count(dev);
   if (sms <= 0) return cuda_fail(cudaGetLastError(), "cudaDeviceGetAttribute");
-  // up to 16 rows: the kernel with fp32 group scaling; more: the wide kernel, 256 rows per pass
+  // up to 16 rows: the kernel with fp32 group scaling; more: the wide kernel, tiles of up to 256 rows,
+  // up to kMaxRowTiles tiles per launch
   const bool wide = M > 16;
-  const int rows = wide ? wide_rows_per_pass() : 16;
-  const int pass_rows = M < rows ? M : rows;
-  long long want = wide ? (long long)sms : (long long)sms * tc5_ctas_per_sm(pass_rows);
+  const int tile = wide ? wide_tile_rows(M) : 16;
+  // CTAs own contiguous ranges of (tile, strip) pairs, so the tiles of a launch are all in flight at once:
+  // keep their activations (tile x K halves each) within a quarter of L2
+  int max_tiles = (int)((32ll << 20) / ((long long)tile * K * 2));
+  if (max_tiles < 1) max_tiles = 1;
+  if (max_tiles > kMaxRowTiles) max_tiles = kMaxRowTiles;
+  const int rows = wide ? tile * max_tiles : 16;                 // rows per launch
+  const int launch_rows = M < rows ? M : rows;
+  const int row_tiles = wide ? (launch_rows + tile - 1) / tile : 1;
+  long long want = wide ? (long long)sms : (long long)sms * tc5_ctas_per_sm(launch_rows);
   const int cap = wide ? kMaxWideCtas : kMaxCtas;
   int ctas = want < cap ? (int)want : cap;
 
@@ -100,14 +108,14 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
   {
     // keep at least ~12 units per CTA (but use every SM) so that few CTAs share a strip
-    const int total_units = strips * units_per_strip(p.geo);
-    int by_work = total_units / (12);
+    const long long total_units = (long long)row_tiles * strips * units_per_strip(p.geo);
+    if (total_units > 0x3fffffff) return FP6M_ERR_PROB_SHAPE;
+    long long by_work = total_units / 12;
     if (by_work < sms) by_work = sms;
-    if (ctas > by_work) ctas = by_work;
-    if (ctas > total_units) ctas = total_units;
+    if (ctas > by_work) ctas = (int)by_work;
+    if (ctas > total_units) ctas = (int)total_units;
   }
-  if (scratch_bytes < (wide ? wide_scratch_bytes(ctas, pass_rows) : tc5_scratch_bytes(ctas, pass_rows))) return FP6M_ERR_SCRATCH;
-  make_schedule(p.geo, ctas, &p.sched);
+  if (scratch_bytes < (wide ? wide_scratch_bytes(ctas, tile) : tc5_scratch_bytes(ctas, launch_rows))) return FP6M_ERR_SCRATCH;
   p.B = static_cast<const uint8_t*>(B);
   p.S = static_cast<const half*>(s);
   p.N = N; p.K = K;
@@ -120,7 +128,9 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
     p.A = static_cast<const half*>(A) + (size_t)m0 * K;
     p.C = static_cast<half*>(C) + (size_t)m0 * N;
     p.M = (M - m0) < rows ? (M - m0) : rows;
-    cudaError_t e = wide ? launch_gemm_wide(p, static_cast<cudaStream_t>(stream)) : launch_gemm_tc5(p, static_cast<cudaStream_t>(stream));
+    p.row_tiles = wide ? (p.M + tile - 1) / tile : 1;
+    make_schedule(p.geo, ctas, &p.sched, p.row_tiles);
+    cudaError_t e = wide ? launch_gemm_wide(p, tile, static_cast<cudaStream_t>(stream)) : launch_gemm_tc5(p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, wide ? "w46_gemm_wide launch" : "w46_gemm_tc5 launch");
   }
   return FP6M_OK;

@@ -143,7 +143,10 @@ struct Schedule {
 // Cost of one unit for the schedule.  The kernels are bound by per-unit instruction work, which does
 // not depend on how many of the strip's 128 columns exist and is only slightly larger for FP6 than
 // for INT4 (measured: CTAs given FP6 units by their byte count finished in half the time).
-FP6M_HD int unit_cost(const Geometry& g, int strip_linear) { return strip_linear < g.strips4 ? 8 : 9; }
+FP6M_HD int unit_cost(const Geometry& g, int strip_linear) {
+  // with several row tiles per launch the strips repeat (virtual strip = tile * strips + strip)
+  return strip_linear % (g.strips4 + g.strips6) < g.strips4 ? 8 : 9;
+}
 
 // First unit u in [u0, u1] such that the weight of [u0, u) is >= target (u1 if never).
 FP6M_HD int unit_at_cost(const Geometry& g, int u0, int u1, long long target) {
@@ -176,10 +179,12 @@ FP6M_HD long long range_cost(const Geometry& g, int u0, int u1) {
   return acc;
 }
 
-inline void make_schedule(const Geometry& g, int ctas, Schedule* out) {
+// `row_tiles` > 1: the launch covers that many tiles of rows of A; the units of tile t follow those of
+// tile t - 1 (virtual strips), so a CTA mostly works on whole strips of one tile.
+inline void make_schedule(const Geometry& g, int ctas, Schedule* out, int row_tiles = 1) {
   if (ctas > kMaxCtas) ctas = kMaxCtas;
   if (ctas < 1) ctas = 1;
-  const int total_units = (g.strips4 + g.strips6) * units_per_strip(g);
+  const int total_units = row_tiles * (g.strips4 + g.strips6) * units_per_strip(g);
   const long long total_cost = range_cost(g, 0, total_units);
   out->ctas = ctas;
   out->total_units = total_units;

@@ -17,6 +17,7 @@ struct MulParams {
   half* C;              // M x N, row-major
   const half* S;        // scales, b200 order
   int M, N, K;
+  int row_tiles;        // wide kernel: tiles of rows of A covered by this launch (virtual strips = row_tiles x strips)
   Geometry geo;
   int* counters;        // one zero-initialised int per strip (the caller's workspace; left untouched)
   unsigned int* epochs;            // scratch header: [0] launch epoch, [1] CTAs of this launch that have read it
@@ -37,10 +38,11 @@ cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 // gemm_wide.cu
 cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUtensorMap* map);
 constexpr int kMaxWideCtas = 192;   // one CTA per SM
+constexpr int kMaxRowTiles = 32;    // 8192 rows of A per launch
 int wide_rows_per_pass();
 int wide_tile_rows(int rows);
 size_t wide_scratch_bytes(int ctas, int rows);
-cudaError_t launch_gemm_wide(const MulParams& p, cudaStream_t stream);
+cudaError_t launch_gemm_wide(const MulParams& p, int tile_rows, cudaStream_t stream);
 
 // dump_operands.cu
 cudaError_t launch_dump_operands(const uint8_t* B, const half* S, half* W, const Geometry& geo, cudaStream_t stream);

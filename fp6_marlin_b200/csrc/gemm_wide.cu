@@ -59,6 +59,11 @@ struct WideCfg {
 };
 
 // INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
+// coordinates {k0, row0}: k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
+__device__ __forceinline__ void tma_load_act_rows(uint32_t dst, const CUtensorMap* map, int k0, int row0, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(k0), "r"(row0), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void expand_int4_scaled(uint32_t q, half2 s, uint32_t* b) {
   uint32_t e[4];
   expand_int4(q, e);
@@ -129,7 +134,8 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       Walk it;
       it.init(U0, U1, ups);
       bool new_strip = true;
-      int strip_lin = U0 / ups;
+      const int nstrips = geo.strips4 + geo.strips6;
+      int strip_lin = (U0 / ups) % nstrips;            // the strip of the virtual strip (row tile x strip)
       const uint8_t* wsrc = nullptr;
       uint32_t unit_bytes = 0;
       int stage = 0;
@@ -153,6 +159,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         if (++stage == S) { stage = 0; phase ^= 1; }
         new_strip = it.next(cnt);
         strip_lin += new_strip;
+        if (strip_lin == nstrips) strip_lin = 0;
       }
     }
   } else if (warp == 1) {
@@ -162,16 +169,19 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       it.init(U0, U1, ups);
       int sa = 0;
       uint32_t aphase = 0;
+      const int nstrips = geo.strips4 + geo.strips6;
+      int vstrip = U0 / ups;
       grid_dependency_wait();                           // A may come from the previous kernel
       while (it.valid()) {
         const int cnt = it.count();
+        const int tile_row0 = (vstrip / nstrips) * NT;
         for (int h = 0; h < cnt; ++h) {
           mbar_wait_bounded<100>(a_empty + 8 * sa, aphase ^ 1, p.status, dead);
           mbar_arrive_expect_tx(a_full + 8 * sa, C::kActUnitBytes);
-          tma_load_act(smem_u32(act_base) + sa * C::kActUnitBytes, &amap, (it.unit + h) * kUnitRows, a_full + 8 * sa);
+          tma_load_act_rows(smem_u32(act_base) + sa * C::kActUnitBytes, &amap, (it.unit + h) * kUnitRows, tile_row0, a_full + 8 * sa);
           if (++sa == RA) { sa = 0; aphase ^= 1; }
         }
-        it.next(cnt);
+        vstrip += it.next(cnt);
       }
     }
   } else if (warp >= 2 && warp < 2 + C::kIssuers) {
@@ -247,14 +257,17 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     const int row0 = team * RPT;
 
     struct Slice {
-      int strip_lin, strip, nq, u0, u1, s_begin;
+      int strip_lin, strip, nq, u0, u1, s_begin, tile_row0;   // strip_lin: the VIRTUAL strip (row tile x strip)
       bool is6, group;
     };
     auto open_slice = [&](int strip_lin, int u) {
       Slice sl;
+      const int nstrips = geo.strips4 + geo.strips6;
+      const int real = strip_lin % nstrips;
       sl.strip_lin = strip_lin;
-      sl.is6 = strip_lin >= geo.strips4;
-      sl.strip = sl.is6 ? strip_lin - geo.strips4 : strip_lin;
+      sl.tile_row0 = (strip_lin / nstrips) * NT;
+      sl.is6 = real >= geo.strips4;
+      sl.strip = sl.is6 ? real - geo.strips4 : real;
       sl.nq = strip_quads(sl.is6 ? geo.n6 : geo.n4, sl.strip);
       sl.group = !sl.is6 && geo.groups > 1;
       sl.s_begin = strip_lin * ups;
@@ -280,7 +293,8 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       if (writes) {
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          if (row0 + m0 + i < p.M) p.C[(size_t)(row0 + m0 + i) * p.N + gcol] = __float2half_rn(v[i] * col_scale);
+          if (sl.tile_row0 + row0 + m0 + i < p.M)
+            p.C[(size_t)(sl.tile_row0 + row0 + m0 + i) * p.N + gcol] = __float2half_rn(v[i] * col_scale);
       }
     };
 
@@ -523,7 +537,7 @@ cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUt
   return cudaSuccess;
 }
 
-int wide_rows_per_pass() { return 256; }
+int wide_rows_per_pass() { return 256; }   // the widest tile
 
 // rows of the MMA tile used for `rows` rows of A
 int wide_tile_rows(int rows) { return rows <= 32 ? 32 : (rows <= 64 ? 64 : (rows <= 128 ? 128 : 256)); }
@@ -532,10 +546,10 @@ size_t wide_scratch_bytes(int ctas, int rows) {
   return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * wide_tile_rows(rows) * kStripCols * sizeof(unsigned long long);
 }
 
-// Runs the GEMM for rows [0, p.M) with 16 < p.M <= 256; the host dispatcher loops over larger M.
-cudaError_t launch_gemm_wide(const MulParams& p, cudaStream_t stream) {
+// Runs the GEMM for rows [0, p.M) in p.row_tiles tiles of `tile_rows` rows; the host dispatcher loops over larger M.
+cudaError_t launch_gemm_wide(const MulParams& p, int tile_rows, cudaStream_t stream) {
   const bool overlap = tc5_get_overlap();
-  switch (wide_tile_rows(p.M)) {
+  switch (tile_rows) {
     case 32: return launch_wide<Wide32>(p, stream, overlap);
     case 64: return launch_wide<Wide64>(p, stream, overlap);
     case 128: return launch_wide<Wide128>(p, stream, overlap);
