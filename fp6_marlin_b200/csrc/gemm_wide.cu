@@ -55,7 +55,8 @@ struct WideCfg {
   static constexpr int kSlotWords = NT * kStripCols;
   static constexpr int kRowsPerTeam = NT / kTeams;     // rows of the accumulator tile a team writes out
   static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-  static_assert(kTmemUsed <= 512 && kRowsPerTeam % 16 == 0 && kStages >= kTeams && kRing >= kTeams, "configuration");
+  static constexpr int kChunk = kRowsPerTeam < 16 ? kRowsPerTeam : 16;   // rows read back per tcgen05.ld
+  static_assert(kTmemUsed <= 512 && (kRowsPerTeam % 16 == 0 || kRowsPerTeam == 8) && kStages >= kTeams && kRing >= kTeams, "configuration");
 };
 
 // INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
@@ -245,7 +246,10 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     // ================================================================== dequantisers (warps kDeqBase..)
     // thread = weight column = TMEM lane; team t expands the segments n = t, t + T, ... of the CTA
     // and writes out rows [t NT/T, (t+1) NT/T) of every slice's accumulator tile
-    constexpr int RPT = C::kRowsPerTeam;
+    constexpr int RPT = C::kRowsPerTeam, CH = C::kChunk;
+    auto tc_ld_chunk = [](uint32_t taddr, float (&v)[CH]) {
+      if constexpr (CH == 8) tc_ld8(taddr, v); else tc_ld16(taddr, v);
+    };
     const int team = (warp - C::kDeqBase) >> 2;
     const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
     const int c = quarter * 32 + lane;               // weight column inside the strip
@@ -288,11 +292,11 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       const int cc_first = p.sched.bound[cc] / ups;
       return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotWords + row0 * kStripCols + c;
     };
-    auto store_rows = [&](const Slice& sl, int m0, const float (&v)[16], float col_scale, bool writes) {
+    auto store_rows = [&](const Slice& sl, int m0, const float (&v)[CH], float col_scale, bool writes) {
       const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
       if (writes) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
+        for (int i = 0; i < CH; ++i)
           if (sl.tile_row0 + row0 + m0 + i < p.M)
             p.C[(size_t)(sl.tile_row0 + row0 + m0 + i) * p.N + gcol] = __float2half_rn(v[i] * col_scale);
       }
@@ -387,27 +391,27 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         slot = slot_of(cta, sl.strip_lin);
       }
 #pragma unroll 1
-      for (int m0 = 0; m0 < RPT; m0 += 16) {
+      for (int m0 = 0; m0 < RPT; m0 += CH) {
         // add the issuers' tiles in issuer order; issuer i took the slice's segments j with
         // (n0_slice + j) % I == i - one that had none keeps a stale tile, which is skipped
-        float v[16];
+        float v[CH];
 #pragma unroll
-        for (int q = 0; q < 16; ++q) v[q] = 0.f;
+        for (int q = 0; q < CH; ++q) v[q] = 0.f;
 #pragma unroll
         for (int i = 0; i < C::kIssuers; ++i) {
           const int first_j = (i - n0_slice % C::kIssuers + C::kIssuers) % C::kIssuers;
           if (first_j < nseg) {
-            float t[16];
-            tc_ld16(d_base + i * NT + m0, t);
+            float t[CH];
+            tc_ld_chunk(d_base + i * NT + m0, t);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] += t[q];
+            for (int q = 0; q < CH; ++q) v[q] += t[q];
           }
         }
         if (whole) {
           store_rows(sl, m0, v, col_scale, writes);
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
+          for (int i = 0; i < CH; ++i)
             st_relaxed_u64(slot + (m0 + i) * kStripCols, ((unsigned long long)tag << 32) | __float_as_uint(v[i]));
         }
       }
@@ -431,22 +435,22 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       const bool writes = c < strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
       const float col_scale = column_scale(sl, writes);
 #pragma unroll 1
-      for (int m0 = 0; m0 < RPT; m0 += 16) {
-        float sum[16];
+      for (int m0 = 0; m0 < RPT; m0 += CH) {
+        float sum[CH];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+        for (int i = 0; i < CH; ++i) sum[i] = 0.f;
         for (int cc = c_lo; cc <= cta; ++cc) {
           if (p.sched.bound[cc] >= p.sched.bound[cc + 1]) continue;
           const unsigned long long* src = slot_of(cc, reduce_strip) + m0 * kStripCols;
-          unsigned long long v[16];
+          unsigned long long v[CH];
           bool all_here = false;
 #pragma unroll 1
           for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = ld_relaxed_u64(src + i * kStripCols);
+            for (int i = 0; i < CH; ++i) v[i] = ld_relaxed_u64(src + i * kStripCols);
             all_here = true;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) all_here = all_here && (uint32_t)(v[i] >> 32) == reduce_tag;
+            for (int i = 0; i < CH; ++i) all_here = all_here && (uint32_t)(v[i] >> 32) == reduce_tag;
             if (dead) break;
           }
           if (!all_here && !dead) {
@@ -454,7 +458,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
             if (p.status) atomicExch(p.status, kStatusTimeout);
           }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sum[i] += __uint_as_float((uint32_t)v[i]);
+          for (int i = 0; i < CH; ++i) sum[i] += __uint_as_float((uint32_t)v[i]);
         }
         store_rows(sl, m0, sum, col_scale, writes);
       }
@@ -469,7 +473,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   }
 }
 
-using Wide32 = WideCfg<32, 2, 4, 8, 8, 6>;      // 4 x 32 + 6 x 64 = 512 TMEM columns
+using Wide32 = WideCfg<32, 4, 4, 8, 8, 6>;      // 4 x 32 + 6 x 64 = 512 TMEM columns
 using Wide64 = WideCfg<64, 4, 4, 8, 8, 4>;      // 4 x 64 + 4 x 64
 using Wide128 = WideCfg<128, 2, 2, 6, 6, 4>;    // 2 x 128 + 4 x 64
 using Wide256 = WideCfg<256, 2, 1, 4, 4, 3>;    // 256 + 3 x 64
