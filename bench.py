@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sweep", action="store_true", help="also time the other M values and layer shapes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: all-gather of the output columns fused into the GEMM epilogue as peer stores, or NCCL")
     ap.add_argument("--only-shape", default=None, metavar="K,N,M",
                     help="time just this shape the way --sweep does and print its record (used for profiling other shapes)")
     ap.add_argument("--no-overlap", action="store_true",
@@ -260,7 +262,18 @@ def b200_arm(args):
     # the previous kernel of the stream drains; activations, outputs and scratch wait for that kernel
     fm.set_launch_overlap(not args.no_overlap)
 
+    exchange = None
+    if world > 1 and args.exchange == "peer":
+        from types import SimpleNamespace
+        exchange = shard.PeerExchange(shard.ShardPlan(N_DIM, QUANT_COLS, world), rank, M_ROWS, dev)
+        shards = [SimpleNamespace(B=B, s=s, quant_cols=qc_local, group_size=GROUP) for B, s in copies]
+
     def step(i, a):
+        if exchange is not None:
+            # every rank stores its columns into every rank's (M, N) output; signal + bounded wait complete the step
+            exchange.mul_scatter(a, shards[i % n_copies], workspace, i % 2)
+            exchange.finish()
+            return
         B, s = copies[i % n_copies]
         fm.mul(a, B, c_dev, s, workspace, qc_local, group_size=GROUP, layout="b200")
         if world > 1:
@@ -273,10 +286,22 @@ def b200_arm(args):
 
     sampler = ClockSampler(str(torch.cuda.get_device_properties(dev).uuid) if rank == 0 else None) if rank == 0 else None
 
+    exchange_ok = None
     with torch.cuda.stream(stream):
         for i in range(max(args.warmup, 3)):
             step(i, a_dev)
         torch.cuda.synchronize()
+        if exchange is not None:
+            # parity of the fused exchange: the same step through the NCCL all-gather + column assembly
+            last = max(args.warmup, 3) - 1
+            B, s = copies[last % n_copies]
+            fm.mul(a_dev, B, c_dev, s, workspace, qc_local, group_size=GROUP, layout="b200")
+            dist.all_gather_into_tensor(gathered, c_dev)
+            expect = shard.assemble(gathered, shard.ShardPlan(N_DIM, QUANT_COLS, world))
+            torch.cuda.synchronize()
+            ok = torch.tensor([int(torch.equal(expect, exchange.outputs[last % 2]))], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            exchange_ok = bool(ok.item())
 
         # ---- value: K steps, captured in CUDA graphs when single-GPU
         chunk = min(GRAPH_CHUNK, args.steps)
@@ -312,7 +337,9 @@ def b200_arm(args):
         for i in range(e2e_steps):
             a_dev.copy_(a_host, non_blocking=True)
             step(i, a_dev)
-            if world > 1:
+            if exchange is not None:
+                c_host.view(M_ROWS, N_DIM).copy_(exchange.outputs[i % 2], non_blocking=True)
+            elif world > 1:
                 c_host.copy_(gathered, non_blocking=True)
             else:
                 c_host[0].copy_(c_dev, non_blocking=True)
@@ -341,14 +368,18 @@ def b200_arm(args):
         "config": {"workload": "cfg1 square layer K=N=8192 M=16 qc=256 INT4-g128", "M": M_ROWS, "K": K_DIM, "N": N_DIM,
                    "quant_cols": QUANT_COLS, "group_size": GROUP,
                    "l2": f"{n_copies} rotating weight copies ({n_copies * weight.B.numel() * 4 / 1e6:.0f} MB) exceed L2",
-                   "parallelism": "single GPU" if world == 1 else f"N-sharded over {world} GPUs + NCCL all-gather of output columns",
+                   "parallelism": "single GPU" if world == 1 else (
+                       f"N-sharded over {world} GPUs, output columns exchanged by peer stores in the GEMM epilogue + signal/wait kernels"
+                       if exchange is not None else f"N-sharded over {world} GPUs + NCCL all-gather of output columns"),
                    "graph": True, "launch_overlap": not args.no_overlap},
         "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": M_ROWS * N_DIM * 2},
-        "gpu_launches": args.steps,
+        "gpu_launches": args.steps * (2 if exchange is not None else 1),
         "clocks": clocks,
         "device_status": status,
     }
+    if exchange_ok is not None:
+        line["config"]["exchange_matches_nccl_all_gather"] = exchange_ok
     if world == 1:
         achieved = nbytes_local / (ms_step * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -369,6 +400,9 @@ def b200_arm(args):
         sys.stdout.flush()
         threading.Timer(20.0, lambda: os._exit(0)).start()
         dist.barrier()
+        if exchange is not None:
+            exchange.close()
+            dist.barrier()
         dist.destroy_process_group()
         os._exit(0)
 

@@ -15,7 +15,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libfp6m.so")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 
-CUDA_SOURCES = ["c_api.cu", "gemm_tc5.cu", "gemm_wide.cu", "dump_operands.cu", "prep_gpu.cu"]
+CUDA_SOURCES = ["c_api.cu", "gemm_tc5.cu", "gemm_wide.cu", "dump_operands.cu", "prep_gpu.cu", "peer.cu"]
 HOST_SOURCES = ["host_pack.cpp"]
 
 NVCC_FLAGS = [

@@ -56,10 +56,14 @@ size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
   return (b + 255) & ~(size_t)255;
 }
 
-int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+}  // extern "C"
+
+namespace {
+
+int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
              void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
              int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
-             int quant_cols, int group_size, int layout, int* status_dev) {
+             int quant_cols, int group_size, int layout, int* status_dev, const OutputMap& out) {
   // --- the checks of the reference dispatcher, in its order (fp6_marlin_cuda_kernel.cu:885-907)
   if (M < 0 || N < 0 || K < 0) return FP6M_ERR_BAD_ARG;
   if (thread_k == -1 || thread_n == -1) {
@@ -80,7 +84,7 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   const int qc = quant_cols < 0 ? 0 : quant_cols;
   if (qc > N || qc % 8 || (N - qc) % 8 || K % 8) return FP6M_ERR_PROB_SHAPE;
   if (group_size == 128 && K % 128) return FP6M_ERR_PROB_SHAPE;
-  if (!A || !B || !C || !s || !workspace || !scratch) return FP6M_ERR_BAD_ARG;
+  if (!A || !B || (!C && out.n_out == 0) || !s || !workspace || !scratch) return FP6M_ERR_BAD_ARG;
   if (!aligned16(A) || !aligned16(B) || !aligned16(C) || !aligned16(s) || !aligned16(scratch)) return FP6M_ERR_BAD_ARG;
 
   DeviceGuard guard(dev);
@@ -123,10 +127,12 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.epochs = static_cast<unsigned int*>(scratch);
   p.partials = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(scratch) + kEpochWords * sizeof(unsigned int));
   p.status = status_dev;
+  p.out = out;
 
   for (int m0 = 0; m0 < M; m0 += rows) {
     p.A = static_cast<const half*>(A) + (size_t)m0 * K;
-    p.C = static_cast<half*>(C) + (size_t)m0 * N;
+    p.C = C ? static_cast<half*>(C) + (size_t)m0 * N : nullptr;
+    for (int q = 0; q < out.n_out; ++q) p.out.peer[q] = out.peer[q] + (size_t)m0 * out.ld;
     p.M = (M - m0) < rows ? (M - m0) : rows;
     p.row_tiles = wide ? (p.M + tile - 1) / tile : 1;
     make_schedule(p.geo, ctas, &p.sched, p.row_tiles);
@@ -134,6 +140,37 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
     if (e != cudaSuccess) return cuda_fail(e, wide ? "w46_gemm_wide launch" : "w46_gemm_tc5 launch");
   }
   return FP6M_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+             void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
+             int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+             int quant_cols, int group_size, int layout, int* status_dev) {
+  OutputMap out = {};
+  return mul_impl(A, B, C, s, M, N, K, workspace, workspace_bytes, scratch, scratch_bytes, dev, stream, thread_k, thread_n,
+                  sms, max_par, quant_cols, group_size, layout, status_dev, out);
+}
+
+int fp6m_mul_scatter(const void* A, const void* B, void* const* outputs, int n_outputs, int ld_out, int col4_base, int col6_base,
+                     const void* s, int M, int N, int K, void* workspace, size_t workspace_bytes, void* scratch,
+                     size_t scratch_bytes, int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+                     int quant_cols, int group_size, int layout, int* status_dev) {
+  if (!outputs || n_outputs < 1 || n_outputs > 8 || ld_out < N || col4_base < 0 || col6_base < 0) return FP6M_ERR_BAD_ARG;
+  OutputMap out = {};
+  out.n_out = n_outputs;
+  out.ld = ld_out;
+  out.col4 = col4_base;
+  out.col6 = col6_base;
+  for (int q = 0; q < n_outputs; ++q) {
+    if (!outputs[q] || (reinterpret_cast<uintptr_t>(outputs[q]) & 1)) return FP6M_ERR_BAD_ARG;
+    out.peer[q] = static_cast<half*>(outputs[q]);
+  }
+  return mul_impl(A, B, nullptr, s, M, N, K, workspace, workspace_bytes, scratch, scratch_bytes, dev, stream, thread_k,
+                  thread_n, sms, max_par, quant_cols, group_size, layout, status_dev, out);
 }
 
 // Scratch of fp6m_mul_static_scratch.  In host code this name is only a handle: the device address

@@ -11,6 +11,17 @@
 
 namespace fp6m {
 
+// Where the results go.  n_out == 0: to C (M x N, this GEMM's own columns).  n_out > 0 (N-sharded layer): the
+// kernel stores every value straight into the full-width output buffers of all ranks (its own included; peer
+// memory mapped through CUDA IPC), at the shard's place among the layer's columns - the all-gather of the output
+// columns happens inside the epilogue, as plain stores over NVLink.
+struct OutputMap {
+  half* peer[8];
+  int n_out;
+  int ld;                // row stride of the full-width outputs = N of the whole layer
+  int col4, col6;        // column of the whole layer where this shard's INT4 / FP6 columns start
+};
+
 struct MulParams {
   const half* A;        // M x K, row-major
   const uint8_t* B;     // packed weights, b200 layout
@@ -23,6 +34,7 @@ struct MulParams {
   unsigned int* epochs;            // scratch header: [0] launch epoch, [1] CTAs of this launch that have read it
   unsigned long long* partials;    // split-K slots (scratch): {fp32 value, epoch tag} per 64-bit word
   int* status;          // optional device status word
+  OutputMap out;
   Schedule sched;
 };
 

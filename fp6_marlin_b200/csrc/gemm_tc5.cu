@@ -302,13 +302,12 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
       const int s_begin = sl.s_begin, s_end = s_begin + ups;
       if (sl.u0 == s_begin && sl.u1 == s_end) {      // the whole strip was ours
         const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
-        const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
         const bool writes = c < ncols;
         const float col_scale = column_scale(sl, writes);
         if (writes) {
 #pragma unroll
           for (int m = 0; m < HN; ++m)
-            if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(out[m] * col_scale);
+            if (row0 + m < p.M) store_result(p, row0 + m, sl.is6, sl.strip * kStripCols + c, out[m] * col_scale);
         }
         return;
       }
@@ -373,13 +372,12 @@ __global__ void __launch_bounds__(C::kThreads, C::kCtasPerSm) w46_gemm_tc5_kerne
         }
       }
       const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
-      const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
       const bool writes = c < ncols;
       const float col_scale = column_scale(sl, writes);
       if (writes) {
 #pragma unroll
         for (int m = 0; m < HN; ++m)
-          if (row0 + m < p.M) p.C[(size_t)(row0 + m) * p.N + gcol] = __float2half_rn(sum[m] * col_scale);
+          if (row0 + m < p.M) store_result(p, row0 + m, sl.is6, sl.strip * kStripCols + c, sum[m] * col_scale);
       }
     };
 

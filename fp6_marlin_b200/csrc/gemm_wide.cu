@@ -293,12 +293,11 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotWords + row0 * kStripCols + c;
     };
     auto store_rows = [&](const Slice& sl, int m0, const float (&v)[CH], float col_scale, bool writes) {
-      const int gcol = (sl.is6 ? geo.n4 : 0) + sl.strip * kStripCols + c;
       if (writes) {
 #pragma unroll
         for (int i = 0; i < CH; ++i)
           if (sl.tile_row0 + row0 + m0 + i < p.M)
-            p.C[(size_t)(sl.tile_row0 + row0 + m0 + i) * p.N + gcol] = __float2half_rn(v[i] * col_scale);
+            store_result(p, sl.tile_row0 + row0 + m0 + i, sl.is6, sl.strip * kStripCols + c, v[i] * col_scale);
       }
     };
 

@@ -1,0 +1,149 @@
+// Peer memory for the N-sharded GEMM: buffers that the other GPUs of the node can store into (CUDA IPC,
+// plain peer stores over NVLink - no multicast), and the two small kernels that turn the per-rank GEMMs
+// into an all-gather: `signal` tells every rank that this rank's shard of step t has landed, `wait`
+// holds the stream until every rank has said so.  Waiting is bounded; a wait that runs out records
+// FP6M_ERR_TIMEOUT in the status word and lets the stream go on.  The reference has no multi-GPU code.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fp6m.h"
+
+namespace {
+
+struct Guard {
+  int prev = -1;
+  explicit Guard(int dev) {
+    cudaGetDevice(&prev);
+    if (dev >= 0 && dev != prev) cudaSetDevice(dev);
+  }
+  ~Guard() {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+struct FlagPointers {
+  int* peer[8];
+};
+
+// One thread.  The GEMM of this step ran before this kernel on the same stream, so its stores to the peers have
+// been issued; the fence orders them before the flags for every observer in the system.
+__global__ void signal_kernel(FlagPointers flags, int n, int rank, int* step) {
+  const int t = *step + 1;
+  *step = t;
+  __threadfence_system();
+  for (int q = 0; q < n; ++q) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.peer[q] + rank), "r"(t) : "memory");
+  }
+}
+
+// n threads: thread r waits until rank r has signalled the step that this rank's signal kernel last started
+__global__ void wait_kernel(const int* flags, int n, const int* step, int* status) {
+  const int r = threadIdx.x;
+  if (r >= n) return;
+  if (status && *status != 0) return;      // an earlier wait already ran out: do not stall every later step
+  const int t = *step;
+  int seen = 0;
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+    if (seen - t >= 0) return;
+    __nanosleep(200);
+  }
+  if (status) atomicExch(status, FP6M_ERR_TIMEOUT);
+}
+
+// Both in one launch: thread 0 signals, then thread r waits for rank r (a launch costs more than the hand-shake).
+__global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* step, int* status) {
+  // the next GEMM of the stream may set itself up and prefetch its weights during the hand-shake; it touches
+  // activations, outputs and scratch only after this kernel has completed (its own griddepcontrol.wait)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ int target;
+  if (threadIdx.x == 0) {
+    const int t = *step + 1;
+    *step = t;
+    target = t;
+    __threadfence_system();
+    for (int q = 0; q < n; ++q) {
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.peer[q] + rank), "r"(t) : "memory");
+    }
+  }
+  __syncthreads();
+  const int r = threadIdx.x;
+  if (r >= n) return;
+  if (status && *status != 0) return;
+  const int t = target;
+  int seen = 0;
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags.peer[rank] + r) : "memory");
+    if (seen - t >= 0) return;
+    __nanosleep(100);
+  }
+  if (status) atomicExch(status, FP6M_ERR_TIMEOUT);
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp6m_peer_alloc(size_t bytes, int dev, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return FP6M_ERR_BAD_ARG;
+  Guard guard(dev);
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return FP6M_ERR_CUDA;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess) { cudaFree(p); return FP6M_ERR_CUDA; }
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) { cudaFree(p); return FP6M_ERR_CUDA; }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  __builtin_memcpy(handle64, &h, 64);
+  *ptr = p;
+  return FP6M_OK;
+}
+
+int fp6m_peer_open(const void* handle64, int dev, void** ptr) {
+  if (!handle64 || !ptr) return FP6M_ERR_BAD_ARG;
+  Guard guard(dev);
+  cudaIpcMemHandle_t h;
+  __builtin_memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return FP6M_ERR_CUDA;
+  *ptr = p;
+  return FP6M_OK;
+}
+
+int fp6m_peer_close(void* ptr, int dev) {
+  Guard guard(dev);
+  return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
+
+int fp6m_peer_free(void* ptr, int dev) {
+  Guard guard(dev);
+  return cudaFree(ptr) == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
+
+int fp6m_peer_signal(void* const* flag_arrays, int n, int rank, int* step_dev, int dev, void* stream) {
+  if (!flag_arrays || n < 1 || n > 8 || rank < 0 || rank >= n || !step_dev) return FP6M_ERR_BAD_ARG;
+  Guard guard(dev);
+  FlagPointers f = {};
+  for (int q = 0; q < n; ++q) f.peer[q] = static_cast<int*>(flag_arrays[q]);
+  signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev);
+  return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
+
+int fp6m_peer_signal_wait(void* const* flag_arrays, int n, int rank, int* step_dev, int* status_dev, int dev, void* stream) {
+  if (!flag_arrays || n < 1 || n > 8 || rank < 0 || rank >= n || !step_dev) return FP6M_ERR_BAD_ARG;
+  Guard guard(dev);
+  FlagPointers f = {};
+  for (int q = 0; q < n; ++q) f.peer[q] = static_cast<int*>(flag_arrays[q]);
+  signal_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev, status_dev);
+  return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
+
+int fp6m_peer_wait(const void* flags_local, int n, const int* step_dev, int* status_dev, int dev, void* stream) {
+  if (!flags_local || n < 1 || n > 8 || !step_dev) return FP6M_ERR_BAD_ARG;
+  Guard guard(dev);
+  wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(flags_local), n, step_dev, status_dev);
+  return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
+
+}  // extern "C"

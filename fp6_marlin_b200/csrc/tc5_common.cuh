@@ -103,6 +103,20 @@ __device__ __forceinline__ uint32_t atomic_add_relaxed_u32(unsigned int* addr, u
   return old;
 }
 
+// ---- result stores ---------------------------------------------------------------------------------
+// `col` is the column inside the shard's INT4 or FP6 region; see OutputMap.
+template <class Params>
+__device__ __forceinline__ void store_result(const Params& p, int row, bool is6, int col, float v) {
+  const half h = __float2half_rn(v);
+  if (p.out.n_out == 0) {
+    p.C[(size_t)row * p.N + (is6 ? p.geo.n4 : 0) + col] = h;
+  } else {
+    const size_t at = (size_t)row * p.out.ld + (is6 ? p.out.col6 : p.out.col4) + col;
+#pragma unroll 1
+    for (int q = 0; q < p.out.n_out; ++q) p.out.peer[q][at] = h;
+  }
+}
+
 // ---- activations by tiled TMA --------------------------------------------------------------------
 // activations of one unit: K-major, 128-byte swizzle (layout type 2), 1024 bytes between 8-row groups;
 // the leading-dimension field is not used by swizzled K-major layouts

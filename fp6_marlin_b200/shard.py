@@ -102,3 +102,108 @@ class ShardedW46Linear:
     def forward(self, a: torch.Tensor) -> torch.Tensor:
         """(M, K) activations (replicated) -> (g, M, N/g) gathered output; `assemble` orders the columns."""
         return all_gather_columns(self.forward_local(a))
+
+
+class _DevicePointer:
+    """Lets torch wrap raw device memory (``torch.as_tensor`` reads ``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class PeerExchange:
+    """Fused exchange step: every rank's GEMM stores its output columns straight into the full-width output
+    buffers of ALL ranks (peer memory over NVLink, mapped with CUDA IPC), in the layer's global column order,
+    and a signal / bounded-wait pair of tiny kernels stands in for the collective.
+
+    ``outputs`` are double-buffered: step t uses buffer t % 2, so a rank that already runs step t + 1 does
+    not overwrite what a slower rank still reads from step t.  Set-up allocates and exchanges IPC handles
+    through ``torch.distributed`` (object all-gather); the hot path (``mul_scatter`` + ``finish``) makes no
+    collective call and is CUDA-graph capturable.
+    """
+
+    def __init__(self, plan: ShardPlan, rank: int, m_max: int, device, group=None):
+        import ctypes
+
+        from ._lib import lib
+        self._lib, self._ct = lib, ctypes
+        self.plan, self.rank, self.world = plan, rank, plan.world
+        self.device = torch.device(device)
+        self.dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.m_max = m_max
+        self.step = 0
+        out_bytes = 2 * m_max * plan.n * 2
+        flag_bytes = 256
+        self._own = []          # (ptr, handle) of this rank's buffers: outputs, flags
+        for nbytes in (out_bytes, flag_bytes):
+            ptr = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            rc = lib.fp6m_peer_alloc(nbytes, self.dev_index, ctypes.byref(ptr), handle)
+            if rc:
+                raise RuntimeError(f"fp6m_peer_alloc failed with code {rc}")
+            self._own.append((ptr.value, handle.raw))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, [h for _, h in self._own], group=group)
+        self._opened = []
+        self.out_ptrs, self.flag_ptrs = [], []
+        for r in range(self.world):
+            if r == rank:
+                self.out_ptrs.append(self._own[0][0])
+                self.flag_ptrs.append(self._own[1][0])
+                continue
+            ptrs = []
+            for h in handles[r]:
+                ptr = ctypes.c_void_p()
+                rc = lib.fp6m_peer_open(ctypes.create_string_buffer(h, 64), self.dev_index, ctypes.byref(ptr))
+                if rc:
+                    raise RuntimeError(f"fp6m_peer_open failed with code {rc} (rank {r})")
+                ptrs.append(ptr.value)
+                self._opened.append(ptr.value)
+            self.out_ptrs.append(ptrs[0])
+            self.flag_ptrs.append(ptrs[1])
+        # this rank's own memory as tensors
+        self.outputs = torch.as_tensor(_DevicePointer(self._own[0][0], (2, m_max, plan.n), "<f2"), device=self.device)
+        self._step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._flag_table = (ctypes.c_void_p * self.world)(*self.flag_ptrs)
+        self._out_tables = [(ctypes.c_void_p * self.world)(*[p + b * m_max * plan.n * 2 for p in self.out_ptrs]) for b in (0, 1)]
+        dist.barrier(group=group)      # every rank has mapped every buffer before anyone stores
+
+    def mul_scatter(self, a, weight, workspace, buffer: int):
+        """Local GEMM of this rank's shard; results go to buffer ``buffer`` (0/1) of every rank."""
+        from . import _lib
+        from .api import _device_buffers, _ptr
+        m, k = a.shape
+        if m > self.m_max:
+            raise ValueError("mul_scatter: more rows than the exchange was built for")
+        _, scratch, status = _device_buffers(self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        plan = self.plan
+        col4 = self.rank * (plan.n4 // plan.world)
+        col6 = plan.n4 + self.rank * plan.qc_local
+        rc = self._lib.fp6m_mul_scatter(_ptr(a), _ptr(weight.B), self._out_tables[buffer], self.world, plan.n, col4, col6,
+                                        _ptr(weight.s), m, plan.n_local, k, _ptr(workspace),
+                                        workspace.numel() * workspace.element_size(), _ptr(scratch), scratch.numel(),
+                                        self.dev_index, stream, -1, -1, -1, 16, weight.quant_cols, weight.group_size,
+                                        _lib.LAYOUT_B200, _ptr(status))
+        if rc:
+            raise RuntimeError(f"fp6m_mul_scatter failed with code {rc}: {_lib.last_cuda_error()}")
+
+    def finish(self):
+        """Signal "my shard has landed everywhere" and hold the stream until every rank has signalled."""
+        from .api import _device_buffers, _ptr
+        _, _, status = _device_buffers(self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.fp6m_peer_signal_wait(self._flag_table, self.world, self.rank, _ptr(self._step_dev), _ptr(status),
+                                             self.dev_index, stream)
+        if rc:
+            raise RuntimeError(f"peer signal/wait failed with code {rc}")
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's; call on every rank after a barrier."""
+        for ptr in self._opened:
+            self._lib.fp6m_peer_close(ptr, self.dev_index)
+        self._opened = []
+        self.outputs = None
+        for ptr, _ in self._own:
+            self._lib.fp6m_peer_free(ptr, self.dev_index)
+        self._own = []

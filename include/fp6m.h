@@ -138,6 +138,37 @@ int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, 
                        int group_size, int dev, void* stream);
 
 /* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
+/* The GEMM of one shard of an N-sharded layer, with the all-gather of the output columns fused into its
+ * epilogue: instead of C, every value is stored into `n_outputs` (1..8) full-width output buffers of `ld_out`
+ * columns - the ranks' own buffer and the peers' buffers mapped with fp6m_peer_open - at column
+ * `col4_base + j` for the shard's INT4 column j and `col6_base + j` for its FP6 column j.  Plain stores over
+ * NVLink, no collective call, no multicast.  Everything else as fp6m_mul.  No counterpart in the reference. */
+int fp6m_mul_scatter(const void* A, const void* B, void* const* outputs, int n_outputs, int ld_out, int col4_base, int col6_base,
+                     const void* s, int M, int N, int K, void* workspace, size_t workspace_bytes, void* scratch,
+                     size_t scratch_bytes, int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+                     int quant_cols, int group_size, int layout, int* status_dev);
+
+/* Peer memory and the hand-shake that completes the fused all-gather.  These ALLOCATE / map device memory
+ * and are meant for set-up and tear-down, not for the hot path:
+ *   fp6m_peer_alloc   cudaMalloc + zero + CUDA IPC handle (64 bytes) to send to the other ranks of the node
+ *   fp6m_peer_open    maps a buffer of another process from its handle (peer access enabled lazily)
+ *   fp6m_peer_close / fp6m_peer_free   undo the two above
+ * Hot path, asynchronous on `stream`, stream-ordered after the GEMM of the step:
+ *   fp6m_peer_signal  increments this rank's device step counter and writes it, with system-scope release,
+ *                     to slot `rank` of every rank's flag array (n arrays of n ints, zero at start)
+ *   fp6m_peer_wait    holds the stream until every slot of this rank's own flag array has reached this rank's
+ *                     step counter; bounded (about a second), then FP6M_ERR_TIMEOUT goes to `status_dev`.
+ * Each rank runs the same sequence GEMM, signal, wait; the outputs should be double-buffered by the caller
+ * (a rank may start writing step t+1 while another still reads step t). */
+int fp6m_peer_alloc(size_t bytes, int dev, void** ptr, void* handle64);
+int fp6m_peer_open(const void* handle64, int dev, void** ptr);
+int fp6m_peer_close(void* ptr, int dev);
+int fp6m_peer_free(void* ptr, int dev);
+int fp6m_peer_signal(void* const* flag_arrays, int n, int rank, int* step_dev, int dev, void* stream);
+int fp6m_peer_wait(const void* flags_local, int n, const int* step_dev, int* status_dev, int dev, void* stream);
+/* fp6m_peer_signal followed by fp6m_peer_wait in one launch (flag_arrays[rank] is this rank's own array). */
+int fp6m_peer_signal_wait(void* const* flag_arrays, int n, int rank, int* step_dev, int* status_dev, int dev, void* stream);
+
 /* Device-side weight preparation.  The reference prepares weights in single-threaded host loops
  * (fp6_marlin/weight_quant.cpp:106-124, fp6_marlin/weight_prepacking.cpp:123-177); these two do the same
  * work on the GPU, asynchronously on `stream`, with device pointers, and produce the same bytes as
