@@ -27,14 +27,20 @@ struct FlagPointers {
   int* peer[8];
 };
 
-// One thread.  The GEMM of this step ran before this kernel on the same stream, so its stores to the peers have
-// been issued; the fence orders them before the flags for every observer in the system.
+// n threads.  The GEMM of this step ran before this kernel on the same stream, so its stores to the peers have
+// been issued; one system-scope fence per thread orders them before the flags, then thread q writes rank q's
+// flag - the n remote stores travel in parallel (a release store per peer from one thread costs one NVLink
+// round trip each: measured 2.4 us per peer).
 __global__ void signal_kernel(FlagPointers flags, int n, int rank, int* step) {
-  const int t = *step + 1;
-  *step = t;
+  __shared__ int target;
+  if (threadIdx.x == 0) {
+    target = *step + 1;
+    *step = target;
+  }
+  __syncthreads();
   __threadfence_system();
-  for (int q = 0; q < n; ++q) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.peer[q] + rank), "r"(t) : "memory");
+  if (threadIdx.x < n) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(flags.peer[threadIdx.x] + rank), "r"(target) : "memory");
   }
 }
 
@@ -60,17 +66,15 @@ __global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* ste
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ int target;
   if (threadIdx.x == 0) {
-    const int t = *step + 1;
-    *step = t;
-    target = t;
-    __threadfence_system();
-    for (int q = 0; q < n; ++q) {
-      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.peer[q] + rank), "r"(t) : "memory");
-    }
+    target = *step + 1;
+    *step = target;
   }
   __syncthreads();
+  __threadfence_system();
   const int r = threadIdx.x;
   if (r >= n) return;
+  // thread r: this rank's flag to rank r (the n remote stores travel in parallel), then wait for rank r's flag
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(flags.peer[r] + rank), "r"(target) : "memory");
   if (status && *status != 0) return;
   const int t = target;
   int seen = 0;
@@ -126,7 +130,7 @@ int fp6m_peer_signal(void* const* flag_arrays, int n, int rank, int* step_dev, i
   Guard guard(dev);
   FlagPointers f = {};
   for (int q = 0; q < n; ++q) f.peer[q] = static_cast<int*>(flag_arrays[q]);
-  signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev);
+  signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev);
   return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
 }
 
