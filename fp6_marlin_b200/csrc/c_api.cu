@@ -111,11 +111,12 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   const int strips = p.geo.strips4 + p.geo.strips6;
   if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
   {
-    // keep at least ~12 units per CTA (but use every SM) so that few CTAs share a strip
+    // at least ~16 units per CTA, also when that leaves SMs idle: a small GEMM split over every SM spends
+    // its time in the split-K reduction (16 contributors per strip for N = 1024), not in streaming
     const long long total_units = (long long)row_tiles * strips * units_per_strip(p.geo);
     if (total_units > 0x3fffffff) return FP6M_ERR_PROB_SHAPE;
-    long long by_work = total_units / 12;
-    if (by_work < sms) by_work = sms;
+    long long by_work = total_units / 16;
+    if (by_work < 1) by_work = 1;
     if (ctas > by_work) ctas = (int)by_work;
     if (ctas > total_units) ctas = (int)total_units;
   }

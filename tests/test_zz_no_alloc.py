@@ -53,7 +53,7 @@ def test_static_scratch_entry_point_matches_mul_twice():
 
 def test_static_scratch_rejects_what_does_not_fit():
     dev = torch.device("cuda:0")
-    m, k, n = 64, 1024, 8192                            # 64 rows on a full grid need more than 16 MiB
+    m, k, n = 64, 4096, 8192                            # 64 rows on a full grid need more than 16 MiB
     w = synth.make_layer(k, n, 256, 128, seed=6, keep_dequantized=False).to(dev)
     a = synth.make_activations(m, k, 6).to(dev)
     c = torch.zeros((m, n), dtype=torch.float16, device=dev)
