@@ -59,12 +59,12 @@ struct WideCfg {
   static_assert(kTmemUsed <= 512 && (kRowsPerTeam % 16 == 0 || kRowsPerTeam == 8) && kStages >= kTeams && kRing >= kTeams, "configuration");
 };
 
-// INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
 // coordinates {k0, row0}: k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
 __device__ __forceinline__ void tma_load_act_rows(uint32_t dst, const CUtensorMap* map, int k0, int row0, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(k0), "r"(row0), "r"(bar) : "memory");
 }
+// INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
 __device__ __forceinline__ void expand_int4_scaled(uint32_t q, half2 s, uint32_t* b) {
   uint32_t e[4];
   expand_int4(q, e);

@@ -59,7 +59,7 @@ __global__ void wait_kernel(const int* flags, int n, const int* step, int* statu
   if (status) atomicExch(status, FP6M_ERR_TIMEOUT);
 }
 
-// Both in one launch: thread 0 signals, then thread r waits for rank r (a launch costs more than the hand-shake).
+// Both in one launch (a launch costs more than the hand-shake): thread r signals rank r, then waits for rank r.
 __global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* step, int* status) {
   // the next GEMM of the stream may set itself up and prefetch its weights during the hand-shake; it touches
   // activations, outputs and scratch only after this kernel has completed (its own griddepcontrol.wait)
