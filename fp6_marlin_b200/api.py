@@ -244,19 +244,37 @@ def schedule(k: int, n: int, quant_cols: int = -1, group_size: int = -1, ctas: i
 # mul
 # ----------------------------------------------------------------------------------------------
 
-_scratch: dict[int, torch.Tensor] = {}
+_scratch: dict[tuple[int, int], torch.Tensor] = {}
 _status: dict[int, torch.Tensor] = {}
+_sm_count: dict[int, int] = {}
 _prepared: dict[int, tuple] = {}
 
 
-def _device_buffers(device: torch.device):
+def _device_buffers(device: torch.device, shape=None):
+    """(device index, split-K scratch, status word) for a GEMM on the CURRENT stream of `device`.
+
+    The scratch holds the launch epoch and the tagged split-K slots of the kernels, so two GEMMs that
+    can overlap on the GPU must not share one: there is one buffer per (device, stream), created (and
+    zeroed, in stream order) the first time a stream is used and grown when a shape needs more.
+    `shape` = (M, N, K, quant_cols) sizes it for that GEMM; None sizes it for any GEMM of up to 16 rows.
+    The reference is re-entrant per stream in the same way: each concurrent call brings its own
+    workspace (fp6_marlin_cuda_kernel.cu:90-93)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _scratch:
-        nbytes = lib.fp6m_mul_scratch_bytes(0, 0, 0, 0, -1)
-        # zero once: the kernel keeps per-strip epoch words and tagged split-K slots in it between calls
-        _scratch[idx] = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    if idx not in _status:
         _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
-    return idx, _scratch[idx], _status[idx]
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    if shape is None:
+        nbytes = lib.fp6m_mul_scratch_bytes(16, 1 << 20, 1 << 14, 0, _sm_count[idx])
+    else:
+        nbytes = lib.fp6m_mul_scratch_bytes(shape[0], shape[1], shape[2], shape[3], _sm_count[idx])
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        # zero once: the kernels keep the epoch and the tagged slots in it between calls
+        with torch.cuda.device(device):
+            buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return idx, buf, _status[idx]
 
 
 def set_launch_overlap(enable: bool) -> bool:
@@ -272,7 +290,10 @@ def device_status(device=None) -> int:
     """Reads (and clears) the device status word: 0, or FP6M_ERR_TIMEOUT (8) if a bounded wait
     inside a kernel ran out since the last call.  Synchronises the device."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    _, _, status = _device_buffers(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        return 0
+    status = _status[idx]
     value = int(status.item())
     if value:
         status.zero_()
@@ -302,6 +323,7 @@ def mul(A, B, C, s, workspace, quant_cols=-1, thread_k=-1, thread_n=-1, sms=-1, 
     A (M, K) fp16, B packed int32, C (M, N) fp16 pre-allocated and overwritten in place, s fp16
     scales, workspace with at least ``N/128*max_par`` zero-filled 4-byte elements (left zero), all
     on one CUDA device; runs asynchronously on the current stream of A's device and returns None.
+    Calls on different streams of one device may overlap: each stream has its own split-K scratch.
     The last ``quant_cols`` columns of B are FP6 (``-1``: none; ``N``: all), and C keeps B's column
     order.  Raises ``RuntimeError`` for the cases the reference raises for: workspace too small,
     ``N % thread_n`` or ``K % thread_k`` non-zero, no kernel for the tile shape.
@@ -336,7 +358,7 @@ def mul(A, B, C, s, workspace, quant_cols=-1, thread_k=-1, thread_n=-1, sms=-1, 
     elif layout != "b200":
         raise RuntimeError(f"mul: unknown layout {layout!r}")
 
-    dev_index, scratch, status = _device_buffers(A.device)
+    dev_index, scratch, status = _device_buffers(A.device, (M, N, K, quant_cols))
     stream = torch.cuda.current_stream(A.device).cuda_stream
     rc = lib.fp6m_mul(_ptr(A), _ptr(B), _ptr(C), _ptr(s), M, N, K,
                       _ptr(workspace), workspace.numel() * workspace.element_size(),

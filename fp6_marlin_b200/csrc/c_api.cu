@@ -43,17 +43,60 @@ struct DeviceGuard {
   ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
 };
 
+// How a GEMM of M rows is cut into launches: kernel, tile of rows, rows per launch, grid.
+struct LaunchPlan {
+  bool wide;        // more than 16 rows: the kernel with scaled operands and tiles of 32..256 rows
+  int tile;         // rows of A per MMA tile
+  int rows;         // rows of A per launch
+  int ctas;         // grid of the first (largest) launch
+};
+
+// `sms` <= 0: the largest grid any device can get (an upper bound for sizing buffers).
+LaunchPlan plan_launches(int M, const Geometry& geo, int sms) {
+  LaunchPlan lp;
+  lp.wide = M > 16;
+  lp.tile = lp.wide ? wide_tile_rows(M) : 16;
+  // CTAs own contiguous ranges of (tile, strip) pairs, so the tiles of a launch are all in flight at once:
+  // keep their activations (tile x K halves each) within a quarter of L2
+  int max_tiles = (int)((32ll << 20) / ((long long)lp.tile * geo.K * 2));
+  if (max_tiles < 1) max_tiles = 1;
+  if (max_tiles > kMaxRowTiles) max_tiles = kMaxRowTiles;
+  lp.rows = lp.wide ? lp.tile * max_tiles : 16;
+  const int launch_rows = M < lp.rows ? M : lp.rows;
+  const int row_tiles = lp.wide ? (launch_rows + lp.tile - 1) / lp.tile : 1;
+  const int cap = lp.wide ? kMaxWideCtas : kMaxCtas;
+  long long want = sms > 0 ? (long long)sms * (lp.wide ? 1 : tc5_ctas_per_sm(launch_rows)) : cap;
+  int ctas = want < cap ? (int)want : cap;
+  // at least ~16 units per CTA, also when that leaves SMs idle: a small GEMM split over every SM spends
+  // its time in the split-K reduction (16 contributors per strip for N = 1024), not in streaming
+  const long long total_units = (long long)row_tiles * (geo.strips4 + geo.strips6) * units_per_strip(geo);
+  long long by_work = total_units / 16;
+  if (by_work < 1) by_work = 1;
+  if (ctas > by_work) ctas = (int)by_work;
+  if (ctas < 1) ctas = 1;
+  lp.ctas = ctas;
+  return lp;
+}
+
+size_t scratch_bytes_of(const LaunchPlan& lp) {
+  const size_t b = lp.wide ? wide_scratch_bytes(lp.ctas, lp.tile) : tc5_scratch_bytes(lp.ctas, 16);
+  return (b + 255) & ~(size_t)255;
+}
+
 }  // namespace
 
 extern "C" {
 
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
-  (void)M; (void)N; (void)K; (void)quant_cols; (void)sms;
-  // upper bound over every configuration: the largest grid with the largest partial tile
-  size_t b = tc5_scratch_bytes(kMaxCtas, 16);
-  const size_t w = wide_scratch_bytes(kMaxWideCtas, wide_rows_per_pass());
-  if (w > b) b = w;
-  return (b + 255) & ~(size_t)255;
+  if (M <= 0 || N <= 0 || K <= 0) {
+    // no shape given: the bound over every configuration (the largest grid with the largest partial tile)
+    size_t b = tc5_scratch_bytes(kMaxCtas, 16);
+    const size_t w = wide_scratch_bytes(kMaxWideCtas, wide_rows_per_pass());
+    if (w > b) b = w;
+    return (b + 255) & ~(size_t)255;
+  }
+  const int qc = quant_cols < 0 ? 0 : (quant_cols > N ? N : quant_cols);
+  return scratch_bytes_of(plan_launches(M, make_geometry(K, N, qc, 128), sms));
 }
 
 }  // extern "C"
@@ -90,37 +133,15 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   DeviceGuard guard(dev);
   if (sms <= 0) sms = sm_count(dev);
   if (sms <= 0) return cuda_fail(cudaGetLastError(), "cudaDeviceGetAttribute");
-  // up to 16 rows: the kernel with fp32 group scaling; more: the wide kernel, tiles of up to 256 rows,
-  // up to kMaxRowTiles tiles per launch
-  const bool wide = M > 16;
-  const int tile = wide ? wide_tile_rows(M) : 16;
-  // CTAs own contiguous ranges of (tile, strip) pairs, so the tiles of a launch are all in flight at once:
-  // keep their activations (tile x K halves each) within a quarter of L2
-  int max_tiles = (int)((32ll << 20) / ((long long)tile * K * 2));
-  if (max_tiles < 1) max_tiles = 1;
-  if (max_tiles > kMaxRowTiles) max_tiles = kMaxRowTiles;
-  const int rows = wide ? tile * max_tiles : 16;                 // rows per launch
-  const int launch_rows = M < rows ? M : rows;
-  const int row_tiles = wide ? (launch_rows + tile - 1) / tile : 1;
-  long long want = wide ? (long long)sms : (long long)sms * tc5_ctas_per_sm(launch_rows);
-  const int cap = wide ? kMaxWideCtas : kMaxCtas;
-  int ctas = want < cap ? (int)want : cap;
-
   MulParams p;
   p.geo = make_geometry(K, N, qc, group_size);
-  const int strips = p.geo.strips4 + p.geo.strips6;
-  if (workspace_bytes < (size_t)strips * 4) return FP6M_ERR_WORKSPACE;
-  {
-    // at least ~16 units per CTA, also when that leaves SMs idle: a small GEMM split over every SM spends
-    // its time in the split-K reduction (16 contributors per strip for N = 1024), not in streaming
-    const long long total_units = (long long)row_tiles * strips * units_per_strip(p.geo);
-    if (total_units > 0x3fffffff) return FP6M_ERR_PROB_SHAPE;
-    long long by_work = total_units / 16;
-    if (by_work < 1) by_work = 1;
-    if (ctas > by_work) ctas = (int)by_work;
-    if (ctas > total_units) ctas = (int)total_units;
-  }
-  if (scratch_bytes < (wide ? wide_scratch_bytes(ctas, tile) : tc5_scratch_bytes(ctas, launch_rows))) return FP6M_ERR_SCRATCH;
+  if ((long long)kMaxRowTiles * (p.geo.strips4 + p.geo.strips6) * units_per_strip(p.geo) > 0x3fffffff) return FP6M_ERR_PROB_SHAPE;
+  // up to 16 rows: the kernel with fp32 group scaling; more: the wide kernel, tiles of up to 256 rows,
+  // up to kMaxRowTiles tiles per launch
+  const LaunchPlan lp = plan_launches(M, p.geo, sms);
+  const bool wide = lp.wide;
+  const int tile = lp.tile, rows = lp.rows, ctas = lp.ctas;
+  if (scratch_bytes < scratch_bytes_of(lp)) return FP6M_ERR_SCRATCH;
   p.B = static_cast<const uint8_t*>(B);
   p.S = static_cast<const half*>(s);
   p.N = N; p.K = K;
@@ -137,6 +158,7 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
     p.M = (M - m0) < rows ? (M - m0) : rows;
     p.row_tiles = wide ? (p.M + tile - 1) / tile : 1;
     make_schedule(p.geo, ctas, &p.sched, p.row_tiles);
+    if (!wide) align_schedule_to_blocks(&p.sched);
     cudaError_t e = wide ? launch_gemm_wide(p, tile, static_cast<cudaStream_t>(stream)) : launch_gemm_tc5(p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, wide ? "w46_gemm_wide launch" : "w46_gemm_tc5 launch");
   }
@@ -161,6 +183,11 @@ int fp6m_mul_scatter(const void* A, const void* B, void* const* outputs, int n_o
                      size_t scratch_bytes, int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
                      int quant_cols, int group_size, int layout, int* status_dev) {
   if (!outputs || n_outputs < 1 || n_outputs > 8 || ld_out < N || col4_base < 0 || col6_base < 0) return FP6M_ERR_BAD_ARG;
+  {
+    // both column ranges must lie inside a row of the outputs: the stores go to peer memory unchecked
+    const int qc = quant_cols < 0 ? 0 : quant_cols;
+    if (qc > N || (long long)col4_base + (N - qc) > ld_out || (long long)col6_base + qc > ld_out) return FP6M_ERR_BAD_ARG;
+  }
   OutputMap out = {};
   out.n_out = n_outputs;
   out.ld = ld_out;

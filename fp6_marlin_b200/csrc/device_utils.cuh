@@ -1,5 +1,5 @@
-// Device-side building blocks for sm_100a: mbarrier + bulk-TMA wrappers with BOUNDED waits,
-// and the in-register dequantisers of the operand dump.
+// Device-side building blocks for sm_100a: mbarrier + bulk-TMA wrappers with BOUNDED waits and
+// small logic / permute helpers.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -111,45 +111,5 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 }
 __device__ __forceinline__ uint32_t h2_as_u32(half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<half2*>(&u); }
-
-// ---- dequantisers -------------------------------------------------------------------------------
-// One INT4 word of the b200 layout (8 rows of one column) -> four half2 = the row pairs
-// (i0,i1), (i2,i3), (i4,i5), (i6,i7), each value exactly fp16(q - 8) * scale with ONE fp16 rounding.
-// q - 8 is built exactly with the 1024-offset trick (0x6400 | nibble = 1024 + nibble), the same
-// values the reference's dequant_8int4 produces (fp6_marlin_cuda_kernel.cu:249-286).
-__device__ __forceinline__ void dequant_int4_word(uint32_t q, half2 scale, uint32_t (&out)[4]) {
-  constexpr uint32_t kLo = 0x000f000f, kHi = 0x00f000f0, kMagic = 0x64006400;
-  constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
-  const half2 sub = u32_as_h2(0x64086408);      // 1032
-  const half2 mul = u32_as_h2(0x2c002c00);      // 1/16
-  const half2 add = u32_as_h2(0xd480d480);      // -72
-  uint32_t lo = lop3<kAndOr>(q, kLo, kMagic);
-  uint32_t hi = lop3<kAndOr>(q, kHi, kMagic);
-  out[0] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lo), sub), scale));
-  out[1] = h2_as_u32(__hmul2(__hfma2(u32_as_h2(hi), mul, add), scale));
-  q >>= 8;
-  lo = lop3<kAndOr>(q, kLo, kMagic);
-  hi = lop3<kAndOr>(q, kHi, kMagic);
-  out[2] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lo), sub), scale));
-  out[3] = h2_as_u32(__hmul2(__hfma2(u32_as_h2(hi), mul, add), scale));
-}
-
-// One FP6 4-bit-plane word plus its 2-bit-plane word (b200 layout) -> four half2, each value the
-// exact E3M2 value times the column scale with ONE fp16 rounding - bit-identical to
-// hmul(hmul(bits, 4096), scale) of dequantMatrix_fp6_to_fp16 (weight_prepacking.cpp:205-212)
-// because `scale4096` = scale * 2^12 is exact.  `rot` = 4 * (jr & 1) selects the word's two sets.
-__device__ __forceinline__ void dequant_fp6_word(uint32_t four, uint32_t two, int rot, half2 scale4096,
-                                                 uint32_t (&out)[4]) {
-  constexpr int kAndOr = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
-  const uint32_t r0 = __funnelshift_l(two, two, rot) & 0x90909090u;
-  const uint32_t r1 = __funnelshift_l(two, two, rot + 2) & 0x90909090u;
-  const uint32_t x0 = lop3<kAndOr>(four, 0x0f0f0f0fu, r0);        // bytes `s00eeemm` of rows i0..i3
-  const uint32_t x1 = lop3<kAndOr>(four >> 4, 0x0f0f0f0fu, r1);   // rows i4..i7
-  out[0] = h2_as_u32(__hmul2(u32_as_h2(prmt(x0, 0u, 0x1404u)), scale4096));
-  out[1] = h2_as_u32(__hmul2(u32_as_h2(prmt(x0, 0u, 0x3424u)), scale4096));
-  out[2] = h2_as_u32(__hmul2(u32_as_h2(prmt(x1, 0u, 0x1404u)), scale4096));
-  out[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(x1, 0u, 0x3424u)), scale4096));
-}
-
 
 }  // namespace fp6m

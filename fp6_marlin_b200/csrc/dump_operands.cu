@@ -1,10 +1,12 @@
 // Debug kernel: expands a packed b200 weight buffer to the plain K x N fp16 matrix W_deq with the
-// device dequantisers of device_utils.cuh (exact q - 8 or exact E3M2 value, times the scale with one
-// fp16 rounding).  A test compares it bit-for-bit with the reference's dequantisation rules
-// (test.py:98 for INT4, weight_prepacking.cpp:199-212 for FP6); the large-M GEMM path feeds exactly
-// these values to the tensor cores.
+// expanders the GEMM kernels themselves use (tc5_common.cuh: exact q - 8 or exact E3M2 value / 4096),
+// times the scale with one fp16 rounding.  A test compares it bit-for-bit with the reference's
+// dequantisation rules (test.py:98 for INT4, weight_prepacking.cpp:199-212 for FP6).  The GEMM for
+// more than 16 rows feeds exactly these values to the tensor cores for group-scaled INT4 columns; in
+// the other cases the kernels feed the unscaled expansion and apply the scale to the fp32 sums.
 #include "device_utils.cuh"
 #include "gemm_params.h"
+#include "tc5_common.cuh"
 
 namespace fp6m {
 
@@ -39,9 +41,9 @@ __global__ void dump_operands_kernel(const uint8_t* __restrict__ B, const half* 
       uint32_t b[4];
       if (is6) {
         const uint32_t two = *reinterpret_cast<const uint32_t*>(base + nq * kInt4UnitQuadBytes + c * 16 + (w8 >> 1) * 4);
-        dequant_fp6_word(word, two, 4 * (w8 & 1), s2, b);
+        expand_fp6_scaled(word, two, 4 * (w8 & 1), s2, b);
       } else {
-        dequant_int4_word(word, s2, b);
+        expand_int4_scaled(word, s2, b);
       }
       for (int i = 0; i < 8; ++i) {
         const int row = unit * kUnitRows + 8 * w8 + i;

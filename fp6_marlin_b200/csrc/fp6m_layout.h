@@ -129,7 +129,7 @@ FP6M_HD int int4_nibble_pos(int i) { return (i & 1) ? 4 + (i >> 1) : (i >> 1); }
 
 // ---------------------------------------------------------------------------------------------
 // Stripe schedule.  Units are ordered strip-major (INT4 strips, then FP6 strips), rows fastest,
-// and weighted by the bytes they stream (2 per INT4 quad, 3 per FP6 quad).  CTA c owns the units
+// and weighted by their cost (unit_cost: 8 per INT4 unit, 9 per FP6 unit).  CTA c owns the units
 // [bound[c], bound[c+1]); a strip that is shared by several CTAs is reduced in fp32 by the last
 // of them to finish.  Replaces the reference's static INT4/FP6 SM split and its stripe
 // arithmetic (fp6_marlin_cuda_kernel.cu:308-408).
@@ -190,6 +190,12 @@ inline void make_schedule(const Geometry& g, int ctas, Schedule* out, int row_ti
   out->total_units = total_units;
   for (int c = 0; c <= ctas; ++c)
     out->bound[c] = c == ctas ? total_units : unit_at_cost(g, 0, total_units, total_cost * c / ctas);
+}
+
+// Moves every inner boundary to a whole block (an even unit): the kernel for up to 16 rows works on
+// 128-row blocks.  The number of units per strip is even, so strips and the total stay aligned.
+inline void align_schedule_to_blocks(Schedule* s) {
+  for (int c = 1; c < s->ctas; ++c) s->bound[c] = (s->bound[c] + 1) & ~1;
 }
 
 }  // namespace fp6m

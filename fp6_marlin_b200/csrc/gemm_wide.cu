@@ -64,13 +64,6 @@ __device__ __forceinline__ void tma_load_act_rows(uint32_t dst, const CUtensorMa
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(k0), "r"(row0), "r"(bar) : "memory");
 }
-// INT4 word -> fp16(q - 8) * s with one rounding (the product of an integer of 4 bits and an fp16 is rounded once)
-__device__ __forceinline__ void expand_int4_scaled(uint32_t q, half2 s, uint32_t* b) {
-  uint32_t e[4];
-  expand_int4(q, e);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) b[i] = h2_as_u32(__hmul2(u32_as_h2(e[i]), s));
-}
 
 template <class C>
 __global__ void __launch_bounds__(C::kThreads, 1)
@@ -535,6 +528,22 @@ cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUt
   const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
+
+// A as a 64 x M x K/64 tensor (K a multiple of 64): one box = 64 halves x `box_rows` rows x 2 units = the
+// activations of one 128-row block as two swizzled tiles, one behind the other; units beyond K and rows
+// beyond M read as zero.
+cudaError_t encode_activation_segment_map(const half* A, int M, int K, int box_rows, CUtensorMap* map) {
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return cudaErrorNotSupported;
+  const cuuint64_t dims[3] = {64, (cuuint64_t)M, (cuuint64_t)(K / 64)};
+  const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 2};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<half*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
   return cudaSuccess;

@@ -27,6 +27,10 @@ struct FlagPointers {
   int* peer[8];
 };
 
+// polls of a flag before a wait gives up (each poll sleeps >= 100 ns: the default is about half a second,
+// inside the ~1 s bound of the GEMM kernels' own waits)
+int g_wait_polls = 1 << 22;
+
 // n threads.  The GEMM of this step ran before this kernel on the same stream, so its stores to the peers have
 // been issued; one system-scope fence per thread orders them before the flags, then thread q writes rank q's
 // flag - the n remote stores travel in parallel (a release store per peer from one thread costs one NVLink
@@ -45,22 +49,22 @@ __global__ void signal_kernel(FlagPointers flags, int n, int rank, int* step) {
 }
 
 // n threads: thread r waits until rank r has signalled the step that this rank's signal kernel last started
-__global__ void wait_kernel(const int* flags, int n, const int* step, int* status) {
+__global__ void wait_kernel(const int* flags, int n, const int* step, int* status, int max_polls) {
   const int r = threadIdx.x;
   if (r >= n) return;
   if (status && *status != 0) return;      // an earlier wait already ran out: do not stall every later step
   const int t = *step;
   int seen = 0;
-  for (int spin = 0; spin < (1 << 22); ++spin) {
+  for (int spin = 0; spin < max_polls; ++spin) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
     if (seen - t >= 0) return;
-    __nanosleep(200);
+    __nanosleep(100);
   }
   if (status) atomicExch(status, FP6M_ERR_TIMEOUT);
 }
 
 // Both in one launch (a launch costs more than the hand-shake): thread r signals rank r, then waits for rank r.
-__global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* step, int* status) {
+__global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* step, int* status, int max_polls) {
   // the next GEMM of the stream may set itself up and prefetch its weights during the hand-shake; it touches
   // activations, outputs and scratch only after this kernel has completed (its own griddepcontrol.wait)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -78,7 +82,7 @@ __global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* ste
   if (status && *status != 0) return;
   const int t = target;
   int seen = 0;
-  for (int spin = 0; spin < (1 << 22); ++spin) {
+  for (int spin = 0; spin < max_polls; ++spin) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags.peer[rank] + r) : "memory");
     if (seen - t >= 0) return;
     __nanosleep(100);
@@ -139,14 +143,20 @@ int fp6m_peer_signal_wait(void* const* flag_arrays, int n, int rank, int* step_d
   Guard guard(dev);
   FlagPointers f = {};
   for (int q = 0; q < n; ++q) f.peer[q] = static_cast<int*>(flag_arrays[q]);
-  signal_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev, status_dev);
+  signal_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev, status_dev, g_wait_polls);
   return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
+
+int fp6m_set_peer_wait_polls(int polls) {
+  const int before = g_wait_polls;
+  if (polls > 0) g_wait_polls = polls;
+  return before;
 }
 
 int fp6m_peer_wait(const void* flags_local, int n, const int* step_dev, int* status_dev, int dev, void* stream) {
   if (!flags_local || n < 1 || n > 8 || !step_dev) return FP6M_ERR_BAD_ARG;
   Guard guard(dev);
-  wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(flags_local), n, step_dev, status_dev);
+  wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(flags_local), n, step_dev, status_dev, g_wait_polls);
   return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
 }
 

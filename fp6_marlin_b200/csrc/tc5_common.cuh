@@ -60,6 +60,15 @@ __device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
 }
+// zeroes kCols (a multiple of 16) TMEM columns of this warp's 32 lanes
+template <int kCols>
+__device__ __forceinline__ void tc_st_zero(uint32_t taddr) {
+  const uint32_t z = 0;
+#pragma unroll
+  for (int c0 = 0; c0 < kCols; c0 += 16)
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
+                 ::"r"(taddr + c0), "r"(z) : "memory");
+}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
@@ -168,6 +177,22 @@ __device__ __forceinline__ void expand_fp6(uint32_t four, uint32_t two, int rot,
   b[1] = prmt(x0, 0u, 0x3424u);
   b[2] = prmt(x1, 0u, 0x1404u);
   b[3] = prmt(x1, 0u, 0x3424u);
+}
+
+// The same expansions times a scale, rounded once to fp16: fp16(q - 8) * s is the dequantised INT4 weight of
+// the reference's rule (test.py:98); (value / 4096) * (s * 4096) equals hmul(hmul(bits, 4096), s) of
+// dequantMatrix_fp6_to_fp16 (weight_prepacking.cpp:205-212) because the factor 4096 is exact.
+__device__ __forceinline__ void expand_int4_scaled(uint32_t q, half2 s, uint32_t* b) {
+  uint32_t e[4];
+  expand_int4(q, e);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = h2_as_u32(__hmul2(u32_as_h2(e[i]), s));
+}
+__device__ __forceinline__ void expand_fp6_scaled(uint32_t four, uint32_t two, int rot, half2 s4096, uint32_t* b) {
+  uint32_t e[4];
+  expand_fp6(four, two, rot, e);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = h2_as_u32(__hmul2(u32_as_h2(e[i]), s4096));
 }
 
 // Walks the units [u0, u1) of a CTA as SEGMENTS: runs of one or two units inside one 128-row block

@@ -144,6 +144,6 @@ def select_outlier_columns(w: torch.Tensor, quant_cols: int) -> torch.Tensor:
     amax = torch.amax(torch.abs(w.float()), dim=0)
     order = torch.sort(amax, descending=True, stable=True)[1]
     outliers = torch.sort(order[:quant_cols])[0]
-    mask = torch.ones(n, dtype=torch.bool)
+    mask = torch.ones(n, dtype=torch.bool, device=w.device)
     mask[outliers] = False
-    return torch.cat([torch.arange(n)[mask], outliers])
+    return torch.cat([torch.arange(n, device=w.device)[mask], outliers])

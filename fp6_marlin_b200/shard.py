@@ -175,9 +175,9 @@ class PeerExchange:
         m, k = a.shape
         if m > self.m_max:
             raise ValueError("mul_scatter: more rows than the exchange was built for")
-        _, scratch, status = _device_buffers(self.device)
-        stream = torch.cuda.current_stream(self.device).cuda_stream
         plan = self.plan
+        _, scratch, status = _device_buffers(self.device, (m, plan.n_local, k, weight.quant_cols))
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         col4 = self.rank * (plan.n4 // plan.world)
         col6 = plan.n4 + self.rank * plan.qc_local
         rc = self._lib.fp6m_mul_scatter(_ptr(a), _ptr(weight.B), self._out_tables[buffer], self.world, plan.n, col4, col6,

@@ -15,13 +15,15 @@ LLAMA2_7B = {"qkv": (4096, 12288), "o_proj": (4096, 4096), "gate_up": (4096, 220
 LLAMA2_70B = {"qkv": (8192, 10240), "o_proj": (8192, 8192), "gate_up": (8192, 57344), "down": (28672, 8192)}
 
 
-def make_weight_fp16(k: int, n: int, quant_cols: int, seed: int = 0) -> torch.Tensor:
-    """fp16 W[k, n] with the outlier columns already moved to the end."""
-    gen = torch.Generator(device="cpu").manual_seed(seed)
-    w = (torch.randn((k, n), generator=gen, dtype=torch.float32) * 0.02)
+def make_weight_fp16(k: int, n: int, quant_cols: int, seed: int = 0, device=None) -> torch.Tensor:
+    """fp16 W[k, n] with the outlier columns already moved to the end.  With a CUDA ``device`` the values
+    are drawn and kept there (another stream of random numbers than on the CPU, equally seeded)."""
+    dev = torch.device("cpu") if device is None else torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    w = (torch.randn((k, n), generator=gen, dtype=torch.float32, device=dev) * 0.02)
     qc = max(quant_cols, 0)
     if qc:
-        cols = torch.randperm(n, generator=gen)[:qc]
+        cols = torch.randperm(n, generator=gen, device=dev)[:qc]
         w[:, cols] *= 8.0
     w = w.half()
     if qc:

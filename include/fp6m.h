@@ -103,8 +103,8 @@ size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms);
  *                   zeroed before its first use (see fp6m_mul_scratch_bytes)
  *   quant_cols      number of FP6 columns (last columns of B); -1 = none
  *   group_size      128 or -1 (per-channel)
- *   layout          FP6M_LAYOUT_B200 (FP6M_LAYOUT_REFERENCE is converted by
- *                   fp6m_repack_from_reference on the host, or fp6m_repack_reference_gpu)
+ *   layout          FP6M_LAYOUT_B200 (tensors in the reference's layout are converted first, on the
+ *                   host, by fp6m_repack_from_reference)
  *   status_dev      optional device int: set to FP6M_ERR_TIMEOUT if a bounded wait ran out
  * Output columns keep the order of B: INT4 columns first, FP6 columns last. */
 int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
@@ -118,8 +118,9 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
  * not acceptable.  The split-K scratch is a static array inside the library (FP6M_STATIC_SCRATCH_BYTES,
  * 16 MiB, resident on every GPU that loads the library until the process exits); the caller still
  * passes A, B, C, s and the workspace.  This entry point has no counterpart in the reference.
- *   - Enough for up to 16 rows of A per call on any grid (larger M fits when `sms` limits the grid);
- *     a call that would need more returns FP6M_ERR_SCRATCH and launches nothing.
+ *   - Enough for up to 16 rows of A per call on grids of up to 511 CTAs, i.e. on every GPU with fewer
+ *     than 512 SMs (larger M fits when `sms` limits the grid); a call that would need more returns
+ *     FP6M_ERR_SCRATCH and launches nothing.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress); make
  *     that first call outside any stream capture.
  *   - All calls share the one array: calls that can overlap on the GPU (different streams) race.
@@ -131,13 +132,13 @@ int fp6m_mul_static_scratch(const void* A, const void* B, void* C, const void* s
                             int thread_k, int thread_n, int sms, int max_par,
                             int quant_cols, int group_size, int layout, int* status_dev);
 
-/* Debug: the fp16 operand tile the kernels feed the tensor cores, W_deq[K, N] row-major, produced by
- * the same device dequantisation routines.  Lets a test prove bit-exactness against the reference
- * dequantisers (dequant_8int4 / dequant_8fp6, fp6_marlin_cuda_kernel.cu:195-286). */
+/* Debug: the dequantised weights W_deq[K, N] (fp16, row-major), produced by the expansion routines the
+ * GEMM kernels use (exact q - 8, exact E3M2 value / 4096) followed by one fp16 multiply by the scale.
+ * Lets a test prove bit-exactness against the reference's dequantisers (dequant_8int4 / dequant_8fp6,
+ * fp6_marlin_cuda_kernel.cu:195-286) and its dequantised weights (test.py:98, weight_prepacking.cpp:199-212). */
 int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, int quant_cols,
                        int group_size, int dev, void* stream);
 
-/* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
 /* The GEMM of one shard of an N-sharded layer, with the all-gather of the output columns fused into its
  * epilogue: instead of C, every value is stored into `n_outputs` (1..8) full-width output buffers of `ld_out`
  * columns - the ranks' own buffer and the peers' buffers mapped with fp6m_peer_open - at column
@@ -166,6 +167,11 @@ int fp6m_peer_close(void* ptr, int dev);
 int fp6m_peer_free(void* ptr, int dev);
 int fp6m_peer_signal(void* const* flag_arrays, int n, int rank, int* step_dev, int dev, void* stream);
 int fp6m_peer_wait(const void* flags_local, int n, const int* step_dev, int* status_dev, int dev, void* stream);
+/* Process-wide: how many times a wait polls a flag (sleeping at least 100 ns in between) before it gives up and
+ * records FP6M_ERR_TIMEOUT; returns the previous value, a value <= 0 only queries.  Default 1 << 22 (about
+ * half a second).  The reference's counterpart, barrier_acquire, spins without limit
+ * (fp6_marlin_cuda_kernel.cu:79-86). */
+int fp6m_set_peer_wait_polls(int polls);
 /* fp6m_peer_signal followed by fp6m_peer_wait in one launch (flag_arrays[rank] is this rank's own array). */
 int fp6m_peer_signal_wait(void* const* flag_arrays, int n, int rank, int* step_dev, int* status_dev, int dev, void* stream);
 
@@ -186,6 +192,7 @@ int fp6m_pack_b200_device(const void* q4, const void* c6, const void* s4, const 
  * reference. */
 int fp6m_set_launch_overlap(int enable);
 
+/* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char* fp6m_last_cuda_error(void);
 
 /* Library version tag, e.g. "fp6m-b200 0.1 (sm_100a)". */

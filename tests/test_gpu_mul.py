@@ -342,7 +342,7 @@ def test_mul_scatter_places_a_shard_in_full_width_outputs(m):
     fm.mul(a, ww.B, c, ww.s, workspace, qc, group_size=gs, layout="b200")
     outs = [torch.full((m, n_total), -7.0, dtype=torch.float16, device=dev) for _ in range(2)]
     table = (ctypes.c_void_p * 2)(*[o.data_ptr() for o in outs])
-    _, scratch, status = api._device_buffers(dev)
+    _, scratch, status = api._device_buffers(dev, (m, n, k, qc))
     rc = _lib.lib.fp6m_mul_scatter(a.data_ptr(), ww.B.data_ptr(), table, 2, n_total, col4, col6, ww.s.data_ptr(), m, n, k,
                                    workspace.data_ptr(), workspace.numel() * 4, scratch.data_ptr(), scratch.numel(), dev.index or 0,
                                    torch.cuda.current_stream(dev).cuda_stream, -1, -1, -1, 16, qc, gs, _lib.LAYOUT_B200,

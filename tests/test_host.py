@@ -45,6 +45,27 @@ def test_drop_in_module_surface():
     assert defaults == [-1, -1, -1, -1, 16]          # fp6_marlin/__init__.py:39
 
 
+def test_extension_module_names_of_the_reference():
+    """``import fp6_marlin_cuda`` / ``import fp6_marlin_cpu`` (the reference's two extension modules,
+    setup.py:38,48; bound names pybind.cpp:89-94 and fp6_marlin_cuda.cpp:125-127) resolve to this library."""
+    import inspect
+
+    import fp6_marlin_cpu
+    import fp6_marlin_cuda
+    for name in ("quantization_cpu", "prepacking_cpu", "dequantization_cpu"):
+        assert callable(getattr(fp6_marlin_cpu, name))
+    sig = inspect.signature(fp6_marlin_cuda.mul)
+    assert list(sig.parameters) == ["A", "B", "C", "s", "workspace", "quant_cols", "thread_k", "thread_n", "sms", "max_par"]
+    assert sig.parameters["max_par"].default == 8     # fp6_marlin_cuda.cpp:57
+    x = torch.zeros((256, 256), dtype=torch.float16)
+    x[0, 0] = 1.5
+    stream = fp6_marlin_cpu.quantization_cpu(x)
+    assert stream.shape == (256, 48) and stream.dtype == torch.int32
+    assert fp6_marlin_cpu.prepacking_cpu(stream).shape == (24, 512)
+    back = fp6_marlin_cpu.dequantization_cpu(stream, torch.ones(256, dtype=torch.float16))
+    assert float(back[0, 0]) == 1.5 and float(back.abs().sum()) == 1.5
+
+
 # ---------------------------------------------------------------- reference-compatible host functions
 def test_host_functions_match_reference_golden(golden_dir):
     g = np.load(os.path.join(golden_dir, "fp6_host_256x256.npz"))
