@@ -7,25 +7,34 @@ values (fp6_marlin_b200/synth.py).  The metric is effective HBM bandwidth: algor
 one GEMM (A + packed weights + scales + C, the form of the reference's bench.py:46-50) divided by
 its latency.
 
-  value      K steps replayed from CUDA graphs (the launch-bound inner loop is captured), inputs
-             resident in HBM, each step on a different one of several weight copies so that the
-             working set exceeds L2; timed with CUDA events on the launching stream.
+  value      the K steps captured in one CUDA graph (the launch-bound inner loop), inputs resident in
+             HBM, each step on a different one of several weight copies so that the working set exceeds
+             L2.  The graph is replayed until at least 0.4 s have been timed (CUDA events on the launching
+             stream around every replay); `ms_per_step` is the median replay divided by K.
   e2e        the same K steps through the public Python API with HOST buffers: every step copies A
              from pinned host memory, calls mul, and copies C back to pinned host memory.
-  roofline   achieved GB/s of the GEMM kernel in the timed region against the measured HBM peak
-             (MEASURED_PEAKS.json), `traffic` from an ncu capture (profiles/).
+  roofline   achieved GB/s of one GPU's GEMM kernel in the timed region against the measured HBM peak
+             (MEASURED_PEAKS.json); `traffic` is the DRAM byte count of one launch from an ncu capture.
+  sweep      (1 GPU) the other points of the configurations: the square layer at M = 1, 16, 64, 128, the
+             Llama-2-7B layers at M = 16 and the compute-bound layer K = N = 16384 at M = 1024, each
+             with latency, GB/s, TFLOP/s, fractions of the measured peaks and a relative Frobenius error
+             of a column subset against the CPU oracle (checker only).
+  multi      (N > 1) GEMM alone / exchange alone / fused per step, a Llama-2-70B gate_up shard at M = 16
+             and, on 8 GPUs, the compute-bound layer at M = 8192.
   cpu_baseline / --impl reference
              the reference's CPU path for the same layer - FP6 columns dequantised by the
              reference's own host code (oracle/_ref), INT4 columns by the rule of its test script
              ((q-8).half()*s), then torch.matmul in fp32 - timed on the host cores.
 
 With N > 1 GPUs (torchrun) the layer's output columns are sharded over the ranks and every step
-ends with an NCCL all-gather of the output columns: total work is fixed ("strong" scaling).
+ends with the all-gather of the output columns (fused into the GEMM epilogue as peer stores, or NCCL):
+total work is fixed ("strong" scaling).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -39,23 +48,26 @@ if ROOT not in sys.path:
 
 K_DIM, N_DIM, M_ROWS, QUANT_COLS, GROUP = 8192, 8192, 16, 256, 128
 METRIC = "W4&6A16 GEMM effective HBM bandwidth (K=N=8192, M=16, 256 FP6 cols, INT4 g128)"
+WORKLOAD = "cfg1 square layer K=N=8192 M=16 qc=256 INT4-g128"
 UNIT = "GB/s"
-GRAPH_CHUNK = 500
-WEIGHT_COPIES = 8          # 8 x 35 MB of packed weights > 2 x the 126 MB L2
+MIN_TIMED_MS = 400.0       # the K-step graph is replayed until this much has been timed
+L2_BYTES = 126e6
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20000)
-    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--sweep", action="store_true", help="also time the other M values and layer shapes")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the other M values and layer shapes (1 GPU)")
+    ap.add_argument("--full-sweep", action="store_true", help="every M of every configuration that fits one GPU")
+    ap.add_argument("--no-multi", action="store_true", help="N > 1: skip the extra shapes and the part timings")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: all-gather of the output columns fused into the GEMM epilogue as peer stores, or NCCL")
-    ap.add_argument("--only-shape", default=None, metavar="K,N,M",
-                    help="time just this shape the way --sweep does and print its record (used for profiling other shapes)")
+    ap.add_argument("--only-shape", default=None, metavar="K,N,M[,qc]",
+                    help="time just this shape the way the sweep does and print its record (used for profiling other shapes)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch the GEMMs without programmatic dependent launch (no overlap of consecutive steps)")
     return ap.parse_args()
@@ -82,8 +94,9 @@ class ClockSampler:
 
     def __init__(self, gpu_uuid: str | None):
         self.rows = []
+        self.marks = []          # (t_begin, t_end) of the timed regions, host clock
         self.proc = None
-        cmd = ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"]
+        cmd = ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"]
         if gpu_uuid:
             cmd += ["-i", gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid]
         try:
@@ -97,39 +110,47 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 9:
-                self.rows.append(parts)
+                self.rows.append((time.perf_counter(), parts))
+
+    def mark(self, t0, t1):
+        self.marks.append((t0, t1))
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, sm_max, reasons = [], [], set()
-        for r in self.rows:
+        sm, sm_max, reasons, in_region = [], [], set(), []
+        for t, r in self.rows:
             try:
-                sm.append(float(r[1]))
+                v = float(r[1])
                 sm_max.append(float(r[2]))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # "under load": samples in the upper half of what was seen (idle samples sit at low clocks)
-        load = [x for x in sm if x >= 0.5 * max(sm)] if sm else []
+            sm.append(v)
+            timed = any(a <= t <= b + 0.06 for a, b in self.marks)
+            if timed:
+                in_region.append(v)
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        # samples taken while a timed region ran; if the sampler missed them all, those in the upper half
+        load = in_region or ([x for x in sm if x >= 0.5 * max(sm)] if sm else [])
         return {"sm_mhz": statistics.median(load) if load else None,
                 "sm_max_mhz": max(sm_max) if sm_max else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_in_timed_regions": len(in_region), "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------------------------------------
-# the reference's CPU path (checker code: the one place bench.py executes oracle/)
+# the reference's CPU path (checker code: bench.py executes oracle/ here and in the sweep's checker)
 # ------------------------------------------------------------------------------------------------
 def cpu_reference_step_fn(n_int4_cols: int):
-    """Returns (step(), algorithmic_bytes, description) for the reference's CPU path on a column slab
-    of the benchmark layer: `n_int4_cols` INT4 columns plus all 256 FP6 columns."""
+    """Returns (step(), algorithmic_bytes, kind, description) for the reference's CPU path on a column
+    slab of the benchmark layer: `n_int4_cols` INT4 columns plus all 256 FP6 columns."""
     import numpy as np
     import torch
 
@@ -176,8 +197,11 @@ def cpu_reference_step_fn(n_int4_cols: int):
 
 
 def time_cpu_reference(steps: int, warmup: int, budget_s: float):
-    """Times the reference's CPU path; sizes the column slab so that the run stays within budget."""
+    """Times the reference's CPU path on all host cores; sizes the column slab so that the run stays
+    within budget."""
     import torch
+    # torchrun exports OMP_NUM_THREADS=1: use the host's cores whatever the launcher set
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     n4_full = N_DIM - QUANT_COLS
     n4 = n4_full
     step, nbytes, kind, desc = cpu_reference_step_fn(n4)
@@ -211,12 +235,265 @@ def reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp16 weights dequantised on the host, fp32 matmul",
-        "data": "synthetic", "config": {"workload": "cfg1 square layer K=N=8192 M=16 qc=256 INT4-g128 (CPU path of the reference)"},
+        "data": "synthetic", "config": {"workload": WORKLOAD, "arm": "CPU path of the reference on the host cores"},
         "cpu_baseline": {"value": res["value"], "unit": UNIT, "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# one layer on N GPUs
+# ------------------------------------------------------------------------------------------------
+class LayerBench:
+    """One W(4&6)A16 layer, N-sharded over the ranks when world > 1, with everything a timed step needs."""
+
+    def __init__(self, env, k, n, m, qc, gs, exchange_kind="peer", seed=0, weight_on_gpu=False, min_copy_bytes=280e6):
+        import torch
+        fm, shard, synth = env["fm"], env["shard"], env["synth"]
+        self.env, self.k, self.n, self.m, self.qc, self.gs = env, k, n, m, qc, gs
+        dev, rank, world = env["dev"], env["rank"], env["world"]
+        self.world = world
+        self.n_local, self.qc_local = n // world, (qc // world if qc > 0 else qc)
+        w = synth.make_weight_fp16(k, n, qc, seed=seed, device=dev if weight_on_gpu else None)
+        self.w_full_fp16 = w if not weight_on_gpu else None
+        self.plan = shard.ShardPlan(n, max(qc, 0), world)
+        if world > 1:
+            w = shard.shard_weight(w, self.plan, rank)
+        self.w_local_fp16 = w
+        weight = fm.make_w46_weight(w, self.qc_local, gs, keep_dequantized=False, quant_device=dev)
+        self.weight = weight
+        per_copy = weight.B.numel() * 4
+        n_copies = max(2, int(min_copy_bytes // per_copy) + 1) if min_copy_bytes > 0 else 1
+        self.copies = [(weight.B.to(dev).clone(), weight.s.to(dev).clone()) for _ in range(n_copies)]
+        self.copy_bytes = n_copies * per_copy
+        self.a_host = synth.make_activations(m, k).pin_memory()
+        self.a_dev = self.a_host.to(dev)
+        self.c_dev = torch.zeros((m, self.n_local), dtype=torch.float16, device=dev)
+        self.gathered = torch.zeros((world, m, self.n_local), dtype=torch.float16, device=dev) if world > 1 else None
+        self.c_host = torch.zeros((m, n), dtype=torch.float16).pin_memory()
+        self.workspace = torch.zeros(max(self.n_local // 128 * 16, 64), dtype=torch.int32, device=dev)
+        self.stream = env["stream"]
+        self.exchange = None
+        self.exchange_kind = exchange_kind if world > 1 else None
+        if world > 1 and exchange_kind == "peer":
+            from types import SimpleNamespace
+            self.exchange = shard.PeerExchange(self.plan, rank, m, dev)
+            self.shards = [SimpleNamespace(B=B, s=s, quant_cols=self.qc_local, group_size=gs) for B, s in self.copies]
+
+    # ---- steps
+    def gemm_only(self, i, a):
+        B, s = self.copies[i % len(self.copies)]
+        self.env["fm"].mul(a, B, self.c_dev, s, self.workspace, self.qc_local, group_size=self.gs, layout="b200")
+
+    def step(self, i, a):
+        import torch.distributed as dist
+        if self.exchange is not None:
+            # every rank stores its columns into every rank's (M, N) output; signal + bounded wait complete the step
+            self.exchange.mul_scatter(a, self.shards[i % len(self.copies)], self.workspace, i % 2)
+            self.exchange.finish()
+            return
+        self.gemm_only(i, a)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, self.c_dev)
+
+    def exchange_only(self, i):
+        import torch.distributed as dist
+        if self.exchange is not None:
+            self.exchange.finish()
+        elif self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, self.c_dev)
+
+    def launches_per_step(self):
+        per_gemm = max(1, -(-self.m // 1024)) if self.m > 16 else 1
+        return per_gemm + (1 if self.exchange is not None else 0)
+
+    # ---- timing
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def time_graph(self, fn, steps, min_ms=MIN_TIMED_MS, max_replays=400, sampler=None):
+        """Captures `steps` calls of fn(i) in one CUDA graph and replays it until min_ms have been timed.
+        Returns the per-replay times in ms (max over ranks for each replay)."""
+        import torch
+        import torch.distributed as dist
+        stream = self.stream
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(steps):
+                fn(i)
+        g.replay()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        g.replay()
+        e1.record(stream)
+        self.barrier()
+        est = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=self.env["dev"])
+        if self.world > 1:
+            dist.all_reduce(est, op=dist.ReduceOp.MAX)
+        replays = int(min(max_replays, max(3, math.ceil(min_ms / max(float(est.item()), 1e-3)))))
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+        self.barrier()
+        t0 = time.perf_counter()
+        events[0].record(stream)
+        for j in range(replays):
+            g.replay()
+            events[j + 1].record(stream)
+        self.barrier()
+        t1 = time.perf_counter()
+        if sampler is not None:
+            sampler.mark(t0, t1)
+        times = torch.tensor([events[j].elapsed_time(events[j + 1]) for j in range(replays)], dtype=torch.float64,
+                             device=self.env["dev"])
+        if self.world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        del g
+        return times.tolist()
+
+    def time_e2e(self, steps, repeats=5):
+        """`steps` steps through the public API with host buffers, host<->device copies inside; median of
+        `repeats` such regions, ms per step (max over ranks)."""
+        import torch
+        import torch.distributed as dist
+        stream = self.stream
+
+        def one(i):
+            self.a_dev.copy_(self.a_host, non_blocking=True)
+            self.step(i, self.a_dev)
+            if self.exchange is not None:
+                self.c_host.copy_(self.exchange.outputs[i % 2], non_blocking=True)
+            elif self.world > 1:
+                self.c_host.view(self.world, self.m, self.n_local).copy_(self.gathered, non_blocking=True)    # rank-major blocks
+            else:
+                self.c_host.copy_(self.c_dev, non_blocking=True)
+
+        for i in range(3):
+            one(i)
+        out = []
+        for _ in range(repeats):
+            self.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                one(i)
+            e1.record(stream)
+            self.barrier()
+            out.append(e0.elapsed_time(e1) / steps)
+        t = torch.tensor(out, dtype=torch.float64, device=self.env["dev"])
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return statistics.median(t.tolist())
+
+    def host_us_per_call(self, calls=2000):
+        """Host time to enqueue one mul (Python + ctypes + tensor-map encoding + launch), device kept busy."""
+        import torch
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(calls):
+            self.gemm_only(i, self.a_dev)
+        t1 = time.perf_counter()
+        torch.cuda.synchronize()
+        return (t1 - t0) / calls * 1e6
+
+    def check_exchange(self, i):
+        """Parity of the fused exchange: the same step through the NCCL all-gather + column assembly."""
+        import torch
+        import torch.distributed as dist
+        shard = self.env["shard"]
+        self.gemm_only(i, self.a_dev)
+        dist.all_gather_into_tensor(self.gathered, self.c_dev)
+        expect = shard.assemble(self.gathered, self.plan)
+        torch.cuda.synchronize()
+        ok = torch.tensor([int(torch.equal(expect, self.exchange.outputs[i % 2]))], device=self.env["dev"])
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        return bool(ok.item())
+
+    def close(self):
+        import torch.distributed as dist
+        if self.exchange is not None:
+            self.barrier()
+            self.exchange.close()
+            dist.barrier()
+            self.exchange = None
+
+
+def oracle_subset_error(env, lb, n_cols=64):
+    """Relative Frobenius error of a column subset of C (first INT4 columns, last FP6 columns) against the
+    CPU oracle: oracle quantisation of those columns of the fp16 weights, fp32-accumulated product.
+    Checker only; the product computes nothing here."""
+    import numpy as np
+    import torch
+    from oracle import formats as F
+    w = lb.w_local_fp16
+    n_loc = lb.n_local
+    qc = max(lb.qc_local, 0)
+    rows = min(lb.m, 16)
+    lb.gemm_only(0, lb.a_dev)
+    torch.cuda.synchronize()
+    c = lb.c_dev[:rows].float().cpu().numpy()
+    a = lb.a_host[:rows].numpy()
+    parts, cols = [], []
+    n4 = min(n_cols, n_loc - qc)
+    if n4 > 0:
+        w4 = w[:, :n4].cpu().numpy()
+        parts.append((F.int4_quantize_group(w4, 128) if lb.gs > 0 else F.int4_quantize_per_channel(w4))[2])
+        cols += list(range(n4))
+    n6 = min(n_cols, qc)
+    if n6 > 0:
+        w6 = w[:, n_loc - n6:].cpu().numpy()
+        parts.append(F.fp6_codes_and_dequant(w6)[2])
+        cols += list(range(n_loc - n6, n_loc))
+    ref = F.gemm_reference(a, np.concatenate(parts, axis=1))
+    return F.rel_frobenius(c[:, cols], ref)
+
+
+def sweep_record(env, tag, k, n, m, qc, peaks, check=True):
+    """Latency / GB/s / TFLOP/s of one shape (graph-timed like `value`) and its oracle check."""
+    synth = env["synth"]
+    lb = LayerBench(env, k, n, m, qc, GROUP, seed=1, weight_on_gpu=True,
+                    min_copy_bytes=(300e6 if m < 1024 else 0))     # large M re-streams B per 256 rows anyway
+    import torch
+    with torch.cuda.stream(env["stream"]):
+        for i in range(3):
+            lb.gemm_only(i, lb.a_dev)
+        torch.cuda.synchronize()
+        err = oracle_subset_error(env, lb) if check else None
+        reps = 100 if m <= 128 else 4
+        times = lb.time_graph(lambda i: lb.gemm_only(i, lb.a_dev), reps, min_ms=60.0, max_replays=50)
+    us = statistics.median(times) * 1e3 / reps
+    nbytes = synth.algorithmic_bytes(m, k, n, qc, GROUP)
+    fl = synth.flops(m, k, n)
+    rec = {"shape": tag, "M": m, "K": k, "N": n, "qc": qc, "us": round(us, 2), "GBs": round(nbytes / us / 1e3, 1),
+           "TFLOPs": round(fl / us / 1e6, 1), "hbm_frac": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
+           "tensor_frac": round(fl / us / 1e6 / peaks["bf16_tflops"], 3),
+           "tensor_frac_sustained": round(fl / us / 1e6 / peaks["bf16_tflops_sustained"], 3)}
+    if err is not None:
+        rec["rel_frobenius_vs_oracle"] = float(f"{err:.3e}")
+    del lb
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run_sweep(env, peaks, full=False, only=None):
+    synth = env["synth"]
+    if only is not None:
+        k, n, m = only[:3]
+        qc = only[3] if len(only) > 3 else QUANT_COLS
+        return [sweep_record(env, "only", k, n, m, qc, peaks)]
+    shapes = [("cfg1", K_DIM, N_DIM, m, QUANT_COLS) for m in ((1, 2, 4, 8, 16, 32, 64, 128) if full else (1, 64, 128))]
+    for name, (k, n) in synth.LLAMA2_7B.items():
+        shapes += [(f"7b_{name}", k, n, m, QUANT_COLS) for m in ((1, 16, 128) if full else (16,))]
+    if full:
+        shapes += [("cfg4", 16384, 16384, m, qc) for m in (1024, 2048, 4096, 8192) for qc in ((0, 128, 256, 512) if m == 1024 else (256,))]
+    else:
+        shapes += [("cfg4", 16384, 16384, 1024, 256)]
+    return [sweep_record(env, tag, k, n, m, qc, peaks) for tag, k, n, m, qc in shapes]
 
 
 # ------------------------------------------------------------------------------------------------
@@ -235,176 +512,135 @@ def b200_arm(args):
     assert torch.cuda.is_available(), "bench.py needs a CUDA GPU (no CPU fallback)"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    peaks = measured_peaks()
+    env = {"fm": fm, "shard": shard, "synth": synth, "dev": dev, "rank": rank, "world": world,
+           "stream": torch.cuda.Stream(device=dev)}
+    # consecutive GEMMs of a decode step: each may set itself up and prefetch its (static) weights while
+    # the previous kernel of the stream drains; activations, outputs and scratch wait for that kernel
+    fm.set_launch_overlap(not args.no_overlap)
     if args.only_shape:
-        k, n, m = (int(x) for x in args.only_shape.split(","))
-        fm.set_launch_overlap(not args.no_overlap)
-        print(json.dumps(run_sweep(fm, synth, dev, measured_peaks(), only=(k, n, m))[0]))
+        only = tuple(int(x) for x in args.only_shape.split(","))
+        env["world"] = 1
+        print(json.dumps(run_sweep(env, peaks, only=only)[0]))
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node == --gpus"
 
-    n_local, qc_local = N_DIM // world, QUANT_COLS // world
-    w = synth.make_weight_fp16(K_DIM, N_DIM, QUANT_COLS, seed=0)
-    if world > 1:
-        w = shard.shard_weight(w, shard.ShardPlan(N_DIM, QUANT_COLS, world), rank)
-    weight = fm.make_w46_weight(w, qc_local, GROUP, keep_dequantized=False, quant_device=dev)
-    n_copies = max(WEIGHT_COPIES, int(280e6 // (weight.B.numel() * 4)) + 1)      # > 2 x L2 in total
-    copies = [(weight.B.to(dev).clone(), weight.s.to(dev).clone()) for _ in range(n_copies)]
-    a_host = synth.make_activations(M_ROWS, K_DIM).pin_memory()
-    a_dev = a_host.to(dev)
-    c_dev = torch.zeros((M_ROWS, n_local), dtype=torch.float16, device=dev)
-    gathered = torch.zeros((world, M_ROWS, n_local), dtype=torch.float16, device=dev) if world > 1 else None
-    c_host = torch.zeros((world, M_ROWS, n_local), dtype=torch.float16).pin_memory()
-    workspace = torch.zeros(max(n_local // 128 * 16, 64), dtype=torch.int32, device=dev)
-    stream = torch.cuda.Stream(device=dev)
-    # consecutive GEMMs of a decode step: each may set itself up and prefetch its (static) weights while
-    # the previous kernel of the stream drains; activations, outputs and scratch wait for that kernel
-    fm.set_launch_overlap(not args.no_overlap)
-
-    exchange = None
-    if world > 1 and args.exchange == "peer":
-        from types import SimpleNamespace
-        exchange = shard.PeerExchange(shard.ShardPlan(N_DIM, QUANT_COLS, world), rank, M_ROWS, dev)
-        shards = [SimpleNamespace(B=B, s=s, quant_cols=qc_local, group_size=GROUP) for B, s in copies]
-
-    def step(i, a):
-        if exchange is not None:
-            # every rank stores its columns into every rank's (M, N) output; signal + bounded wait complete the step
-            exchange.mul_scatter(a, shards[i % n_copies], workspace, i % 2)
-            exchange.finish()
-            return
-        B, s = copies[i % n_copies]
-        fm.mul(a, B, c_dev, s, workspace, qc_local, group_size=GROUP, layout="b200")
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, c_dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+    lb = LayerBench(env, K_DIM, N_DIM, M_ROWS, QUANT_COLS, GROUP, exchange_kind=args.exchange, seed=0)
+    multi = None
+    with torch.cuda.stream(env["stream"]):
+        for i in range(warmup):
+            lb.step(i, lb.a_dev)
         torch.cuda.synchronize()
-
-    sampler = ClockSampler(str(torch.cuda.get_device_properties(dev).uuid) if rank == 0 else None) if rank == 0 else None
-
-    exchange_ok = None
-    with torch.cuda.stream(stream):
-        for i in range(max(args.warmup, 3)):
-            step(i, a_dev)
-        torch.cuda.synchronize()
-        if exchange is not None:
-            # parity of the fused exchange: the same step through the NCCL all-gather + column assembly
-            last = max(args.warmup, 3) - 1
-            B, s = copies[last % n_copies]
-            fm.mul(a_dev, B, c_dev, s, workspace, qc_local, group_size=GROUP, layout="b200")
-            dist.all_gather_into_tensor(gathered, c_dev)
-            expect = shard.assemble(gathered, shard.ShardPlan(N_DIM, QUANT_COLS, world))
-            torch.cuda.synchronize()
-            ok = torch.tensor([int(torch.equal(expect, exchange.outputs[last % 2]))], device=dev)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-            exchange_ok = bool(ok.item())
-
-        # ---- value: K steps, captured in CUDA graphs when single-GPU
-        chunk = min(GRAPH_CHUNK, args.steps)
-        graphs = []
-        if True:
-            for count in ([chunk] if args.steps % chunk == 0 else [chunk, args.steps % chunk]):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    for i in range(count):
-                        step(i, a_dev)
-                graphs.append((g, count))
-            graphs[0][0].replay()
-        barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record(stream)
-        for _ in range(args.steps // chunk):
-            graphs[0][0].replay()
-        if args.steps % chunk:
-            graphs[1][0].replay()
-        ev1.record(stream)
-        barrier()
-        ms_total = ev0.elapsed_time(ev1)
-
-        # ---- e2e: host buffers, copies inside the timed region
-        e2e_steps = args.steps
-        for i in range(3):
-            a_dev.copy_(a_host, non_blocking=True)
-            step(i, a_dev)
-            c_host[0].copy_(c_dev, non_blocking=True)
-        barrier()
-        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev2.record(stream)
-        for i in range(e2e_steps):
-            a_dev.copy_(a_host, non_blocking=True)
-            step(i, a_dev)
-            if exchange is not None:
-                c_host.view(M_ROWS, N_DIM).copy_(exchange.outputs[i % 2], non_blocking=True)
-            elif world > 1:
-                c_host.copy_(gathered, non_blocking=True)
-            else:
-                c_host[0].copy_(c_dev, non_blocking=True)
-        ev3.record(stream)
-        barrier()
-        ms_e2e_total = ev2.elapsed_time(ev3)
-
+        exchange_ok = lb.check_exchange(warmup - 1) if lb.exchange is not None else None
+        times = lb.time_graph(lambda i: lb.step(i, lb.a_dev), steps, sampler=sampler)
+        ms_e2e = lb.time_e2e(steps)
+        host_us = lb.host_us_per_call() if world == 1 else None
+        if world > 1 and not args.no_multi:
+            multi = multi_gpu_extras(env, lb, args, peaks)
     clocks = sampler.stop() if sampler else None
     status = fm.device_status(dev)
 
-    if world > 1:
-        t = torch.tensor([ms_total, ms_e2e_total], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e_total = t.tolist()
-
-    nbytes = synth.algorithmic_bytes(M_ROWS, K_DIM, N_DIM, QUANT_COLS, GROUP)          # whole layer
-    nbytes_local = synth.algorithmic_bytes(M_ROWS, K_DIM, n_local, qc_local, GROUP)     # one rank's kernel
-    ms_step = ms_total / args.steps
-    ms_e2e = ms_e2e_total / e2e_steps
-    peaks = measured_peaks()
+    nbytes = synth.algorithmic_bytes(M_ROWS, K_DIM, N_DIM, QUANT_COLS, GROUP)                      # whole layer
+    nbytes_local = synth.algorithmic_bytes(M_ROWS, K_DIM, lb.n_local, max(lb.qc_local, 0), GROUP)   # one rank's kernel
+    ms_step = statistics.median(times) / steps
     value = nbytes / (ms_step * 1e-3) / 1e9
+    achieved = nbytes_local / (ms_step * 1e-3) / 1e9
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
-        "data": "synthetic",
-        "config": {"workload": "cfg1 square layer K=N=8192 M=16 qc=256 INT4-g128", "M": M_ROWS, "K": K_DIM, "N": N_DIM,
-                   "quant_cols": QUANT_COLS, "group_size": GROUP,
-                   "l2": f"{n_copies} rotating weight copies ({n_copies * weight.B.numel() * 4 / 1e6:.0f} MB) exceed L2",
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "M": M_ROWS, "K": K_DIM, "N": N_DIM, "quant_cols": QUANT_COLS, "group_size": GROUP,
+                   "l2": f"{len(lb.copies)} rotating weight copies ({lb.copy_bytes / 1e6:.0f} MB) exceed L2",
                    "parallelism": "single GPU" if world == 1 else (
                        f"N-sharded over {world} GPUs, output columns exchanged by peer stores in the GEMM epilogue + signal/wait kernels"
-                       if exchange is not None else f"N-sharded over {world} GPUs + NCCL all-gather of output columns"),
-                   "graph": True, "launch_overlap": not args.no_overlap},
+                       if lb.exchange is not None else f"N-sharded over {world} GPUs + NCCL all-gather of output columns"),
+                   "graph": True, "launch_overlap": not args.no_overlap,
+                   "timing": f"graph of {steps} steps replayed {len(times)} times; median replay / steps",
+                   "ms_per_step_min": min(times) / steps, "ms_per_step_max": max(times) / steps},
         "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": M_ROWS * N_DIM * 2},
-        "gpu_launches": args.steps * (2 if exchange is not None else 1),
+                "h2d_bytes_per_step": lb.a_host.numel() * 2, "d2h_bytes_per_step": M_ROWS * N_DIM * 2},
+        "gpu_launches": steps * len(times) * lb.launches_per_step(),
+        "gpu_launches_per_step": lb.launches_per_step(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "peak_source": f"of {peaks['source']}",
+                     "algorithmic_bytes": nbytes_local, "per": "GPU" if world > 1 else "launch",
+                     "traffic": read_traffic_from_profile() if world == 1 else None},
         "clocks": clocks,
         "device_status": status,
     }
+    if host_us is not None:
+        line["e2e"]["host_us_per_mul_call"] = host_us
     if exchange_ok is not None:
         line["config"]["exchange_matches_nccl_all_gather"] = exchange_ok
-    if world == 1:
-        achieved = nbytes_local / (ms_step * 1e-3) / 1e9
-        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                            "frac": achieved / peaks["hbm_gbs"], "peak_source": f"of {peaks['source']}",
-                            "algorithmic_bytes": nbytes_local, "traffic": read_traffic_from_profile()}
+    if multi is not None:
+        line["multi"] = multi
+    lb.close()
+    del lb
+    torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cb = time_cpu_reference(steps=5, warmup=1, budget_s=25.0)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    if args.sweep and world == 1:
-        line["sweep"] = run_sweep(fm, synth, dev, peaks)
+    if world == 1 and not args.no_sweep:
+        with torch.cuda.stream(env["stream"]):
+            line["sweep"] = run_sweep(env, peaks, full=args.full_sweep)
+        line["device_status"] = line["device_status"] or fm.device_status(dev)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         # CUDA graphs that captured NCCL work must go before the communicator does; a watchdog ends the
         # process if the tear-down of the process group stalls (the result line is already printed)
-        graphs.clear()
         torch.cuda.synchronize()
         sys.stdout.flush()
         threading.Timer(20.0, lambda: os._exit(0)).start()
         dist.barrier()
-        if exchange is not None:
-            exchange.close()
-            dist.barrier()
         dist.destroy_process_group()
         os._exit(0)
+
+
+def multi_gpu_extras(env, lb, args, peaks):
+    """N > 1: where a step's time goes for the headline layer, plus the shapes where sharding divides real
+    work: a Llama-2-70B gate_up layer at M = 16 and (8 GPUs) the compute-bound layer at M = 8192."""
+    import torch
+    synth = env["synth"]
+    world = env["world"]
+    out = {}
+    reps = 200
+    t_gemm = statistics.median(lb.time_graph(lambda i: lb.gemm_only(i, lb.a_dev), reps, min_ms=100.0)) * 1e3 / reps
+    t_xchg = statistics.median(lb.time_graph(lambda i: lb.exchange_only(i), reps, min_ms=50.0)) * 1e3 / reps
+    t_fused = statistics.median(lb.time_graph(lambda i: lb.step(i, lb.a_dev), reps, min_ms=100.0)) * 1e3 / reps
+    out["headline_parts_us"] = {"gemm_us": t_gemm, "exchange_us": t_xchg, "fused_us": t_fused,
+                                "exchange": lb.exchange_kind}
+
+    def shape_record(tag, k, n, m, qc, reps, min_ms):
+        b = LayerBench(env, k, n, m, qc, GROUP, exchange_kind=args.exchange, seed=2, weight_on_gpu=True,
+                       min_copy_bytes=(300e6 if m <= 128 else 0))
+        for i in range(3):
+            b.step(i, b.a_dev)
+        torch.cuda.synchronize()
+        ok = b.check_exchange(2) if b.exchange is not None else None
+        tg = statistics.median(b.time_graph(lambda i: b.gemm_only(i, b.a_dev), reps, min_ms=min_ms)) * 1e3 / reps
+        tf = statistics.median(b.time_graph(lambda i: b.step(i, b.a_dev), reps, min_ms=min_ms)) * 1e3 / reps
+        nbytes_local = synth.algorithmic_bytes(m, k, b.n_local, max(b.qc_local, 0), GROUP)
+        fl = synth.flops(m, k, n)
+        rec = {"shape": tag, "M": m, "K": k, "N": n, "qc": qc, "gemm_us": tg, "fused_us": tf,
+               "aggregate_GBs": world * nbytes_local / tf / 1e3, "aggregate_TFLOPs": fl / tf / 1e6,
+               "per_gpu_hbm_frac": nbytes_local / tf / 1e3 / peaks["hbm_gbs"],
+               "per_gpu_tensor_frac": fl / world / tf / 1e6 / peaks["bf16_tflops"],
+               "exchange_matches_nccl_all_gather": ok}
+        b.close()
+        del b
+        torch.cuda.empty_cache()
+        return rec
+
+    k, n = synth.LLAMA2_70B["gate_up"]
+    out["cfg3_70b_gate_up_m16"] = shape_record("70b_gate_up", k, n, 16, QUANT_COLS, 100, 60.0)
+    if world == 8:
+        out["cfg4_m8192"] = shape_record("cfg4", 16384, 16384, 8192, QUANT_COLS, 2, 60.0)
+    return out
 
 
 def read_traffic_from_profile():
@@ -414,55 +650,6 @@ def read_traffic_from_profile():
         with open(path) as f:
             return json.load(f).get("dram_bytes_per_launch_full_size")
     return None
-
-
-def run_sweep(fm, synth, dev, peaks, only=None):
-    """Latency / GB/s / TFLOP/s of other shapes (graph-timed like `value`); extra information."""
-    import torch
-    out = []
-    shapes = [("cfg1", K_DIM, N_DIM, m) for m in (1, 2, 4, 8, 16, 32, 64, 128)]
-    for name, (k, n) in synth.LLAMA2_7B.items():
-        shapes += [(f"7b_{name}", k, n, m) for m in (1, 16, 128)]
-    shapes += [("cfg4", 16384, 16384, m) for m in (1024, 4096)]      # tensor-bound: compare with the bf16 GEMM peak
-    if only is not None:
-        shapes = [("only",) + tuple(only)]
-    cache = {}
-    for tag, k, n, m in shapes:
-        if (k, n) not in cache:
-            cache.clear()
-            wt = synth.make_layer(k, n, QUANT_COLS, GROUP, seed=1, keep_dequantized=False, quant_device=dev)
-            ncopies = max(2, int(300e6 // (wt.B.numel() * 4)) + 1) if m < 1024 else 1   # large M re-streams B per 256 rows anyway
-            cache[(k, n)] = [(wt.B.to(dev).clone(), wt.s.to(dev).clone()) for _ in range(ncopies)]
-        copies = cache[(k, n)]
-        a = synth.make_activations(m, k).to(dev)
-        c = torch.zeros((m, n), dtype=torch.float16, device=dev)
-        ws = torch.zeros(n // 128 * 16, dtype=torch.int32, device=dev)
-        stream = torch.cuda.Stream(device=dev)
-        with torch.cuda.stream(stream):
-            for i in range(5):
-                fm.mul(a, *copies[i % len(copies)][:1], c, copies[i % len(copies)][1], ws, QUANT_COLS, group_size=GROUP, layout="b200")
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            reps = 200 if m <= 128 else 4
-            with torch.cuda.graph(g, stream=stream):
-                for i in range(reps):
-                    B, s = copies[i % len(copies)]
-                    fm.mul(a, B, c, s, ws, QUANT_COLS, group_size=GROUP, layout="b200")
-            g.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(5):
-                g.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (5 * reps)
-        nbytes = synth.algorithmic_bytes(m, k, n, QUANT_COLS, GROUP)
-        fl = synth.flops(m, k, n)
-        out.append({"shape": tag, "M": m, "K": k, "N": n, "us": us, "GBs": nbytes / us / 1e3, "TFLOPs": fl / us / 1e6,
-                    "hbm_frac": nbytes / us / 1e3 / peaks["hbm_gbs"],
-                    "tensor_frac_sustained": fl / us / 1e6 / peaks["bf16_tflops_sustained"]})
-    return out
 
 
 def main():

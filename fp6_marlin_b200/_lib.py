@@ -10,11 +10,13 @@ import ctypes
 import os
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libfp6m.so")
+# FP6M_LIB selects another build of the same library (e.g. the timeline build, see build.py --trace)
+LIB_PATH = os.environ.get("FP6M_LIB") or os.path.join(_PKG_DIR, "libfp6m.so")
 
 OK, ERR_PROB_SHAPE, ERR_KERN_SHAPE, ERR_VALUE_RANGE, ERR_BAD_ARG = 0, 1, 2, 3, 4
 ERR_WORKSPACE, ERR_SCRATCH, ERR_CUDA, ERR_TIMEOUT = 5, 6, 7, 8
 LAYOUT_REFERENCE, LAYOUT_B200 = 0, 1
+EPILOGUE_NONE, EPILOGUE_SILU_MUL, EPILOGUE_RESIDUAL = 0, 1, 2
 
 # every symbol include/fp6m.h declares, with its ctypes signature
 _vp, _sz, _i, _i64 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int64
@@ -33,6 +35,8 @@ SIGNATURES = {
     "fp6m_mul_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "fp6m_mul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp, _sz, _i, _vp,
                       _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "fp6m_mul_fused": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp, _sz, _i, _vp,
+                            _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "fp6m_mul_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _i, _vp,
                                      _i, _i, _i, _i, _i, _i, _i, _vp]),
     "fp6m_dump_operands": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -50,6 +54,7 @@ SIGNATURES = {
     "fp6m_encode_fp6_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]),
     "fp6m_pack_b200_device": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2 + [ctypes.c_int, ctypes.c_void_p]),
     "fp6m_set_launch_overlap": (ctypes.c_int, [ctypes.c_int]),
+    "fp6m_set_ordered_sums": (ctypes.c_int, [ctypes.c_int]),
     "fp6m_last_cuda_error": (ctypes.c_char_p, []),
     "fp6m_version": (ctypes.c_char_p, []),
 }

@@ -286,6 +286,13 @@ def set_launch_overlap(enable: bool) -> bool:
     return bool(lib.fp6m_set_launch_overlap(1 if enable else 0))
 
 
+def set_ordered_sums(enable: bool) -> bool:
+    """Process-wide switch (off by default); returns the previous setting.  When on, the GEMM for up to 16
+    rows adds the products of a 128-row block in one fixed order, so two runs on the same inputs agree bit
+    for bit; when off, the two 64-row halves of a block may be added in either order (faster)."""
+    return bool(lib.fp6m_set_ordered_sums(1 if enable else 0))
+
+
 def device_status(device=None) -> int:
     """Reads (and clears) the device status word: 0, or FP6M_ERR_TIMEOUT (8) if a bounded wait
     inside a kernel ran out since the last call.  Synchronises the device."""
@@ -375,6 +382,54 @@ def mul(A, B, C, s, workspace, quant_cols=-1, thread_k=-1, thread_n=-1, sms=-1, 
     if rc == _lib.ERR_CUDA:
         raise RuntimeError(f"fp6m_mul: CUDA error: {_lib.last_cuda_error()}")
     raise RuntimeError(f"fp6m_mul failed with code {rc}")
+
+
+def mul_fused(A, B, C, s, workspace, quant_cols=-1, *, epilogue="none", residual=None, sms=-1, max_par=16,
+              group_size=-1):
+    """``mul`` (b200 layout only) with the step that follows the GEMM in a transformer block fused into its
+    epilogue, applied to the fp32 sums before the single rounding to fp16:
+
+    ``epilogue="silu_mul"``  gate / up projection: B holds the two projections interleaved - columns 2j and
+                             2j+1 of the INT4 region, and of the FP6 region, are gate_j and up_j (see
+                             :func:`fp6_marlin_b200.make_gate_up_weight`) - and C, of shape (M, N/2),
+                             receives ``silu(gate_j) * up_j``: INT4 pairs first, then FP6 pairs.
+    ``epilogue="residual"``  ``C = A @ W + residual`` with ``residual`` an (M, N) fp16 tensor (it may be C).
+
+    The reference only scales and stores (write_result, fp6_marlin_cuda_kernel.cu:698-749); the layers on
+    either side of its GEMM are the ones its benchmark lists (bench.py:53-86).
+    """
+    code = {"none": _lib.EPILOGUE_NONE, "silu_mul": _lib.EPILOGUE_SILU_MUL, "residual": _lib.EPILOGUE_RESIDUAL}.get(epilogue)
+    if code is None:
+        raise ValueError(f"mul_fused: unknown epilogue {epilogue!r}")
+    if not A.is_cuda:
+        raise RuntimeError("fp6_marlin_b200.mul_fused needs CUDA tensors: there is no CPU implementation")
+    M, K = A.shape
+    N = C.shape[1] * 2 if code == _lib.EPILOGUE_SILU_MUL else C.shape[1]
+    if workspace.numel() < N // 128 * max_par:
+        raise RuntimeError(f"workspace must be of size at least {N // 128 * max_par}.")
+    if A.dtype != torch.float16 or C.dtype != torch.float16 or s.dtype != torch.float16:
+        raise RuntimeError("mul_fused: A, C and s must be float16")
+    if not (A.is_contiguous() and C.is_contiguous() and B.is_contiguous() and s.is_contiguous()):
+        raise RuntimeError("mul_fused: tensors must be contiguous")
+    if C.shape[0] != M:
+        raise RuntimeError("mul_fused: C must have as many rows as A")
+    res_ptr = 0
+    if code == _lib.EPILOGUE_RESIDUAL:
+        if residual is None or residual.dtype != torch.float16 or tuple(residual.shape) != (M, N) or not residual.is_contiguous():
+            raise RuntimeError("mul_fused: residual must be a contiguous float16 tensor of C's shape")
+        res_ptr = _ptr(residual)
+    if M == 0 or N == 0 or K == 0:
+        return
+    dev_index, scratch, status = _device_buffers(A.device, (M, N, K, quant_cols))
+    stream = torch.cuda.current_stream(A.device).cuda_stream
+    rc = lib.fp6m_mul_fused(_ptr(A), _ptr(B), _ptr(C), _ptr(s), M, N, K,
+                            _ptr(workspace), workspace.numel() * workspace.element_size(),
+                            _ptr(scratch), scratch.numel(), dev_index, stream,
+                            -1, -1, sms, max_par, quant_cols, group_size, _lib.LAYOUT_B200, _ptr(status), code, res_ptr)
+    if rc == _lib.ERR_CUDA:
+        raise RuntimeError(f"fp6m_mul_fused: CUDA error: {_lib.last_cuda_error()}")
+    if rc:
+        raise RuntimeError(f"fp6m_mul_fused failed with code {rc}")
 
 
 def dump_operands(B: torch.Tensor, s: torch.Tensor, k: int, n: int, quant_cols: int = -1, group_size: int = -1):

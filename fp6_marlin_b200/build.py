@@ -1,7 +1,7 @@
 """Builds fp6_marlin_b200/libfp6m.so in-tree with nvcc for sm_100a (no GPU needed to compile).
 
-Usage:  python fp6_marlin_b200/build.py [--force] [--verbose]   (run as a script: it must work
-before the package itself can be imported)
+Usage:  python fp6_marlin_b200/build.py [--force] [--verbose] [--trace]   (run as a script: it must
+work before the package itself can be imported)
 """
 from __future__ import annotations
 
@@ -43,18 +43,22 @@ def needs_build() -> bool:
     return any(os.path.getmtime(s) > lib_time for s in _sources())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every source to an object and link the shared library; returns its path."""
-    if not force and not needs_build():
-        return LIB_PATH
-    os.makedirs(OBJ_DIR, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """Compile every source to an object and link the shared library; returns its path.
+    ``trace=True`` builds libfp6m_trace.so instead: the same library with the in-kernel timeline of
+    csrc/trace.cuh compiled in (read by ``python -m fp6_marlin_b200.timeline``)."""
+    lib_path = os.path.join(PKG_DIR, "libfp6m_trace.so") if trace else LIB_PATH
+    obj_dir = OBJ_DIR + ("_trace" if trace else "")
+    if not force and not trace and not needs_build():
+        return lib_path
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     objs, procs = [], []
     log = []
     for src in CUDA_SOURCES + HOST_SOURCES:
-        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DFP6M_TRACE"] if trace else []), "-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, proc in procs:
@@ -62,15 +66,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
         log.append(f"==== {src}\n{out}")
         failed |= proc.returncode != 0
     text = "\n".join(log)
-    with open(os.path.join(OBJ_DIR, "ptxas.log"), "w") as f:
+    with open(os.path.join(obj_dir, "ptxas.log"), "w") as f:
         f.write(text)
     if failed or verbose:
         print(text)
     if failed:
         raise RuntimeError("nvcc failed; see output above")
-    subprocess.run([nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart"], check=True)
-    return LIB_PATH
+    subprocess.run([nvcc, "-shared", "-o", lib_path, *objs, "-lcudart"], check=True)
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

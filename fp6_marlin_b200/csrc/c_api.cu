@@ -54,14 +54,14 @@ struct LaunchPlan {
 // `sms` <= 0: the largest grid any device can get (an upper bound for sizing buffers).
 LaunchPlan plan_launches(int M, const Geometry& geo, int sms) {
   LaunchPlan lp;
-  lp.wide = M > 16;
-  lp.tile = lp.wide ? wide_tile_rows(M) : 16;
+  lp.wide = M > kTc5MaxRows;
+  lp.tile = lp.wide ? wide_tile_rows(M) : tc5_tile_rows(M);
   // CTAs own contiguous ranges of (tile, strip) pairs, so the tiles of a launch are all in flight at once:
   // keep their activations (tile x K halves each) within a quarter of L2
   int max_tiles = (int)((32ll << 20) / ((long long)lp.tile * geo.K * 2));
   if (max_tiles < 1) max_tiles = 1;
   if (max_tiles > kMaxRowTiles) max_tiles = kMaxRowTiles;
-  lp.rows = lp.wide ? lp.tile * max_tiles : 16;
+  lp.rows = lp.wide ? lp.tile * max_tiles : lp.tile;
   const int launch_rows = M < lp.rows ? M : lp.rows;
   const int row_tiles = lp.wide ? (launch_rows + lp.tile - 1) / lp.tile : 1;
   const int cap = lp.wide ? kMaxWideCtas : kMaxCtas;
@@ -70,7 +70,10 @@ LaunchPlan plan_launches(int M, const Geometry& geo, int sms) {
   // at least ~16 units per CTA, also when that leaves SMs idle: a small GEMM split over every SM spends
   // its time in the split-K reduction (16 contributors per strip for N = 1024), not in streaming
   const long long total_units = (long long)row_tiles * (geo.strips4 + geo.strips6) * units_per_strip(geo);
-  long long by_work = total_units / 16;
+#ifndef FP6M_MIN_UNITS_PER_CTA
+#define FP6M_MIN_UNITS_PER_CTA 16
+#endif
+  long long by_work = total_units / FP6M_MIN_UNITS_PER_CTA;
   if (by_work < 1) by_work = 1;
   if (ctas > by_work) ctas = (int)by_work;
   if (ctas < 1) ctas = 1;
@@ -79,7 +82,7 @@ LaunchPlan plan_launches(int M, const Geometry& geo, int sms) {
 }
 
 size_t scratch_bytes_of(const LaunchPlan& lp) {
-  const size_t b = lp.wide ? wide_scratch_bytes(lp.ctas, lp.tile) : tc5_scratch_bytes(lp.ctas, 16);
+  const size_t b = lp.wide ? wide_scratch_bytes(lp.ctas, lp.tile) : tc5_scratch_bytes(lp.ctas, lp.tile);
   return (b + 255) & ~(size_t)255;
 }
 
@@ -90,7 +93,7 @@ extern "C" {
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
   if (M <= 0 || N <= 0 || K <= 0) {
     // no shape given: the bound over every configuration (the largest grid with the largest partial tile)
-    size_t b = tc5_scratch_bytes(kMaxCtas, 16);
+    size_t b = tc5_scratch_bytes(kMaxCtas, kTc5MaxRows);
     const size_t w = wide_scratch_bytes(kMaxWideCtas, wide_rows_per_pass());
     if (w > b) b = w;
     return (b + 255) & ~(size_t)255;
@@ -106,7 +109,8 @@ namespace {
 int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
              void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
              int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
-             int quant_cols, int group_size, int layout, int* status_dev, const OutputMap& out) {
+             int quant_cols, int group_size, int layout, int* status_dev, const OutputMap& out,
+             int epilogue = kEpilogueNone, const void* residual = nullptr) {
   // --- the checks of the reference dispatcher, in its order (fp6_marlin_cuda_kernel.cu:885-907)
   if (M < 0 || N < 0 || K < 0) return FP6M_ERR_BAD_ARG;
   if (thread_k == -1 || thread_n == -1) {
@@ -115,7 +119,7 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   if (thread_k <= 0 || thread_n <= 0) return FP6M_ERR_KERN_SHAPE;
   if (N % thread_n != 0 || K % thread_k != 0) return FP6M_ERR_PROB_SHAPE;
   if (M == 0 || N == 0 || K == 0) return FP6M_OK;
-  // kernels exist for 128x128 tiles with at most 16 rows and for 64x256 tiles (:933-942)
+  // the reference has kernels for 128x128 tiles with at most 16 rows and for 64x256 tiles (:933-942)
   const bool shape_ok = (thread_k == 128 && thread_n == 128 && M <= 16) || (thread_k == 64 && thread_n == 256);
   if (!shape_ok) return FP6M_ERR_KERN_SHAPE;
 
@@ -129,6 +133,9 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   if (group_size == 128 && K % 128) return FP6M_ERR_PROB_SHAPE;
   if (!A || !B || (!C && out.n_out == 0) || !s || !workspace || !scratch) return FP6M_ERR_BAD_ARG;
   if (!aligned16(A) || !aligned16(B) || !aligned16(C) || !aligned16(s) || !aligned16(scratch)) return FP6M_ERR_BAD_ARG;
+  if (epilogue != kEpilogueNone && epilogue != kEpilogueSiluMul && epilogue != kEpilogueResidual) return FP6M_ERR_BAD_ARG;
+  if (epilogue != kEpilogueNone && out.n_out != 0) return FP6M_ERR_BAD_ARG;       // not together with the scattered output
+  if (epilogue == kEpilogueResidual && (!residual || (reinterpret_cast<uintptr_t>(residual) & 1))) return FP6M_ERR_BAD_ARG;
 
   DeviceGuard guard(dev);
   if (sms <= 0) sms = sm_count(dev);
@@ -150,10 +157,14 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.partials = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(scratch) + kEpochWords * sizeof(unsigned int));
   p.status = status_dev;
   p.out = out;
+  p.epilogue = epilogue;
+  p.R = nullptr;
 
   for (int m0 = 0; m0 < M; m0 += rows) {
     p.A = static_cast<const half*>(A) + (size_t)m0 * K;
-    p.C = C ? static_cast<half*>(C) + (size_t)m0 * N : nullptr;
+    // with the gate / up epilogue C has N / 2 columns
+    p.C = C ? static_cast<half*>(C) + (size_t)m0 * (epilogue == kEpilogueSiluMul ? N / 2 : N) : nullptr;
+    p.R = epilogue == kEpilogueResidual ? static_cast<const half*>(residual) + (size_t)m0 * N : nullptr;
     for (int q = 0; q < out.n_out; ++q) p.out.peer[q] = out.peer[q] + (size_t)m0 * out.ld;
     p.M = (M - m0) < rows ? (M - m0) : rows;
     p.row_tiles = wide ? (p.M + tile - 1) / tile : 1;
@@ -176,6 +187,15 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
   OutputMap out = {};
   return mul_impl(A, B, C, s, M, N, K, workspace, workspace_bytes, scratch, scratch_bytes, dev, stream, thread_k, thread_n,
                   sms, max_par, quant_cols, group_size, layout, status_dev, out);
+}
+
+int fp6m_mul_fused(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+                   void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
+                   int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+                   int quant_cols, int group_size, int layout, int* status_dev, int epilogue, const void* residual) {
+  OutputMap out = {};
+  return mul_impl(A, B, C, s, M, N, K, workspace, workspace_bytes, scratch, scratch_bytes, dev, stream, thread_k, thread_n,
+                  sms, max_par, quant_cols, group_size, layout, status_dev, out, epilogue, residual);
 }
 
 int fp6m_mul_scatter(const void* A, const void* B, void* const* outputs, int n_outputs, int ld_out, int col4_base, int col6_base,
@@ -240,6 +260,12 @@ int fp6m_dump_operands(const void* B, const void* s, void* W_out, int N, int K, 
 int fp6m_set_launch_overlap(int enable) {
   const int before = tc5_get_overlap() ? 1 : 0;
   if (enable >= 0) tc5_set_overlap(enable != 0);
+  return before;
+}
+
+int fp6m_set_ordered_sums(int enable) {
+  const int before = tc5_get_ordered_sums() ? 1 : 0;
+  if (enable >= 0) tc5_set_ordered_sums(enable != 0);
   return before;
 }
 

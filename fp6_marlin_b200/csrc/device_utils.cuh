@@ -40,41 +40,129 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// try_wait with a suspend-time hint: the hardware may park the thread until the phase completes or
-// the hint (nanoseconds) runs out, instead of burning issue slots in a polling loop.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0;
-}
-
 // Wait with a limit (about one second).  When the limit runs out the thread records
 // FP6M_ERR_TIMEOUT in *status, marks itself `dead` and carries on as if the wait had succeeded:
 // every address the kernels form is independent of loaded data, so the kernel still terminates
 // (with garbage results and a status the host reads) instead of hanging the GPU.  A dead thread
 // skips all later waits.
-// Bounded wait.  `kSleepNs` > 0 is for roles that run far ahead of their consumers (producers): they
-// sleep between polls, so their polling does not take issue slots from the working warps.
-template <int kSleepNs = 0>
+// A failed mbarrier.try_wait comes back after well under 100 ns on this hardware, so a warp that
+// polls in a plain loop issues instructions all the time and takes issue slots from the warps that
+// work (measured: four in ten of a kernel's executed instructions were polling).  Hence the loop
+// sleeps between polls: `kSleepNs` is the grain - short where the wake-up latency adds to a chain
+// the pipeline depends on, long for roles that run far ahead of their consumers.
+template <int kSleepNs = 32>
 __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, bool& dead) {
-  // fast path: one potentially-blocking try_wait; in steady state the phase is complete already
+  // fast path: in steady state the phase is complete already
   if (mbar_try_wait(bar, parity)) return;
   if (dead) return;
-#pragma unroll 1
-  for (int i = 0; i < (1 << 16); ++i) {                      // up to 65536 x (16 us + sleep)
-    if (kSleepNs > 0) __nanosleep(kSleepNs);
-    if (mbar_try_wait_hint(bar, parity, 16384u)) return;
-  }
+  constexpr uint32_t kSleep = kSleepNs > 0 ? kSleepNs : 1;
+  constexpr uint32_t kLimit = 1u << 24;                       // x (sleep + poll) of at least ~60 ns each: about a second
+  uint32_t ok;
+#ifndef FP6M_WAIT_MODE
+#define FP6M_WAIT_MODE 0
+#endif
+#if FP6M_WAIT_MODE == 0
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .u32 i;\n"
+      "mov.u32 i, 0;\n"
+      "FP6M_WAIT_LOOP:\n"
+      "nanosleep.u32 %3;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "@p bra FP6M_WAIT_DONE;\n"
+      "add.u32 i, i, 1;\n"
+      "setp.lt.u32 p, i, %4;\n"
+      "@p bra FP6M_WAIT_LOOP;\n"
+      "setp.ne.u32 p, 0, 0;\n"
+      "FP6M_WAIT_DONE:\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "n"(kSleep), "n"(kLimit)
+      : "memory");
+#elif FP6M_WAIT_MODE == 1
+  // no sleep; try_wait with a long suspend-time hint
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .u32 i;\n"
+      "mov.u32 i, 0;\n"
+      "FP6M_WAIT_LOOP:\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "@p bra FP6M_WAIT_DONE;\n"
+      "add.u32 i, i, 1;\n"
+      "setp.lt.u32 p, i, %4;\n"
+      "@p bra FP6M_WAIT_LOOP;\n"
+      "setp.ne.u32 p, 0, 0;\n"
+      "FP6M_WAIT_DONE:\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(1000000u), "n"(kLimit)
+      : "memory");
+#else
+  // long sleeps (4 x the grain) between polls
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .u32 i;\n"
+      "mov.u32 i, 0;\n"
+      "FP6M_WAIT_LOOP:\n"
+      "nanosleep.u32 %3;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "@p bra FP6M_WAIT_DONE;\n"
+      "add.u32 i, i, 1;\n"
+      "setp.lt.u32 p, i, %4;\n"
+      "@p bra FP6M_WAIT_LOOP;\n"
+      "setp.ne.u32 p, 0, 0;\n"
+      "FP6M_WAIT_DONE:\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "n"(kSleep * 6), "n"(kLimit)
+      : "memory");
+#endif
+  if (ok) return;
   dead = true;
   if (status) atomicExch(status, kStatusTimeout);
+}
+
+// The same bounded wait without a branch in the caller: the common case - the phase is complete - costs
+// the try_wait and one branch inside the block.  `w.limit` is the number of polls still allowed (a wait
+// that ran out sets it to 1, so that later waits of the thread give up at once) and `w.failed` remembers
+// that a wait ran out; the role reports it once, at its end (report_waits).
+struct WaitState {
+  uint32_t limit = 1u << 24;      // x (sleep + poll) of at least ~60 ns each: about a second
+  uint32_t failed = 0;
+};
+template <int kSleepNs = 32>
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, WaitState& w) {
+  constexpr uint32_t kSleep = kSleepNs > 0 ? kSleepNs : 1;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .u32 i;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%2], %3;\n"
+      "@p bra FP6M_WAIT_DONE;\n"
+      "mov.u32 i, 0;\n"
+      "FP6M_WAIT_LOOP:\n"
+      "nanosleep.u32 %4;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%2], %3;\n"
+      "@p bra FP6M_WAIT_DONE;\n"
+      "add.u32 i, i, 1;\n"
+      "setp.lt.u32 p, i, %0;\n"
+      "@p bra FP6M_WAIT_LOOP;\n"
+      "mov.u32 %0, 1;\n"
+      "mov.u32 %1, 1;\n"
+      "FP6M_WAIT_DONE:\n"
+      "}\n"
+      : "+r"(w.limit), "+r"(w.failed)
+      : "r"(bar), "r"(parity), "n"(kSleep)
+      : "memory");
+}
+__device__ __forceinline__ void report_waits(const WaitState& w, int* status) {
+  if (w.failed && status) atomicExch(status, kStatusTimeout);
 }
 
 // ---- bulk TMA (1-D, global -> shared of this CTA, completion on an mbarrier) -------------------
@@ -95,6 +183,10 @@ __device__ __forceinline__ uint64_t make_evict_first_policy() {
 // ---- named barrier among a subset of warps ---------------------------------------------------
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // ---- logic / permute helpers -------------------------------------------------------------------

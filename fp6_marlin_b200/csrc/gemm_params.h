@@ -22,10 +22,22 @@ struct OutputMap {
   int col4, col6;        // column of the whole layer where this shard's INT4 / FP6 columns start
 };
 
+// What happens to the fp32 sums (times the column scale) before they are rounded to fp16 and stored.
+enum Epilogue {
+  kEpilogueNone = 0,
+  // gate / up projection pairs: columns 2j and 2j + 1 of each region hold gate_j and up_j; C has N / 2
+  // columns and receives silu(gate_j) * up_j, INT4 pairs first, then FP6 pairs
+  kEpilogueSiluMul = 1,
+  // C = A W + R with R an M x N fp16 matrix laid out like C (R may be C itself)
+  kEpilogueResidual = 2,
+};
+
 struct MulParams {
   const half* A;        // M x K, row-major
   const uint8_t* B;     // packed weights, b200 layout
-  half* C;              // M x N, row-major
+  half* C;              // M x N (M x N / 2 with kEpilogueSiluMul), row-major
+  const half* R;        // kEpilogueResidual: the matrix to add
+  int epilogue;         // Epilogue
   const half* S;        // scales, b200 order
   int M, N, K;
   int row_tiles;        // wide kernel: tiles of rows of A covered by this launch (virtual strips = row_tiles x strips)
@@ -42,9 +54,13 @@ constexpr int kEpochWords = 64;     // scratch header size in 32-bit words
 
 // gemm_tc5.cu
 int tc5_ctas_per_sm(int rows);
+int tc5_tile_rows(int rows);
+constexpr int kTc5MaxRows = 64;     // rows of A the kernel of gemm_tc5.cu covers; more rows go to gemm_wide.cu
 size_t tc5_scratch_bytes(int ctas, int rows);
 void tc5_set_overlap(bool on);
 bool tc5_get_overlap();
+void tc5_set_ordered_sums(bool on);
+bool tc5_get_ordered_sums();
 cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 
 // gemm_wide.cu

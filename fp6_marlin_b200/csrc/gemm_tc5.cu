@@ -33,11 +33,13 @@
 //               FP6 codes become `s 00eee mm` fp16 patterns (exact value / 4096, as dequant_8fp6
 //               builds them before its multiply by 4096, :195-237).  A team never waits for an MMA of
 //               its own segment: it goes straight on to its next one.
-//   warps 20-23 epilogue: one warp per TMEM lane quarter.  Every segment has its own accumulator
-//               tile; the epilogue warps read each tile back (tcgen05.ld), multiply by the column's
-//               group scale in fp32 and add to registers - one set of sums per CTA, in segment order.
-//               At the end of a slice (the CTA's blocks of one strip) they write C (column scale in
-//               fp32, one rounding to fp16) or a split-K partial.
+//   warps 20-27 epilogue: two sets of four warps (one warp per TMEM lane quarter); set e takes the
+//               segments n = e, e + 2, ...  Every segment has its own accumulator tile; an epilogue warp
+//               reads the tile back (tcgen05.ld), multiplies by the column's group scale in fp32 and
+//               adds to registers.  At the end of a slice (the CTA's blocks of one strip) set 1 hands its
+//               sums to set 0 through shared memory, and set 0 writes C (column scale in fp32, one
+//               rounding to fp16) or a split-K partial.  (One set alone needs ~700 cycles per segment:
+//               its chain wait - load - wait - add is serial.)
 // Rings: 15 weight stages, 6 {operand slot, activation tile, accumulator tile} entries.  Both ring sizes
 // are multiples of the number of teams, so a stage or an entry always belongs to the same team and every
 // waiter of an mbarrier observes each of its phases in turn (a parity wait that skipped a phase would
@@ -69,16 +71,23 @@ namespace fp6m {
 
 namespace {
 
-template <int NT_, int STAGES_, int RING_, int TEAMS_>
+template <int NT_, int STAGES_, int RING_, int TEAMS_, bool SPLIT_ISSUE_>
 struct Tc5Cfg {
   static constexpr int kTeams = TEAMS_;
-  static constexpr int kIssuers = 2 * TEAMS_;          // one per team and unit
+  // Two issuers per team.  kSplitIssue: both work on every segment of the team, one 64-row unit each, adding to
+  // a tile the team zeroed - the order in which the tensor core retires the two units is not fixed, so the last
+  // bit of a sum may differ from run to run.  Otherwise they take the team's segments in turn, eight MMAs each:
+  // one issuing thread per tile, a fixed order of additions, bit-identical results from run to run.
+  static constexpr bool kSplitIssue = SPLIT_ISSUE_;
+  static constexpr int kIssuers = 2 * TEAMS_;
   // warp 0: weights producer, warp 1: activations producer, warps 2.. : MMA issuers, then (from a
   // multiple of four, so that warp % 4 is the TMEM lane quarter) four dequantiser warps per team and
   // the four epilogue warps
   static constexpr int kDeqBase = (2 + kIssuers + 3) & ~3;
   static constexpr int kEpiBase = kDeqBase + 4 * kTeams;
-  static constexpr int kThreads = 32 * (kEpiBase + 4);
+  static constexpr int kEpiSets = 2;
+  static constexpr int kThreads = 32 * (kEpiBase + 4 * kEpiSets);
+  static_assert(STAGES_ <= 4 * kTeams + 4 * kEpiSets, "the first round of weight copies is issued by one warp per stage");
   static constexpr int kEpochWarp = 2 + kIssuers - 1;
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kStages = STAGES_;              // shared-memory stages of packed words (one segment each)
@@ -89,9 +98,17 @@ struct Tc5Cfg {
   // A stage and a ring entry must always belong to the same team: then every waiter of a barrier sees
   // each of its phases (a team that came back to a barrier two phases later would pass a parity wait early).
   static_assert(kStages % kTeams == 0 && kRing % kTeams == 0, "ring sizes must be multiples of the number of teams");
-  static_assert(kStages <= kEpiBase + 3 - kDeqBase, "the first round of weight copies is issued by one warp per stage");
+
   static_assert(kRing <= kIssuers, "the first round of activation copies is issued by one issuer warp per entry");
-  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kNumBars * 8 + 64 + 1024;   // + alignment slack
+  static_assert(kRing == 2 * kTeams, "each team owns two ring entries (one per issuer when the issuers take turns)");
+  static constexpr int kScaleRingBytes = kRing * kStripCols * 4;   // the group scale (fp16 bits in a word) of every column of the segment in a ring entry
+  // Up to 16 rows the two epilogue sets take the segments in turn and pool their sums at the end of a slice;
+  // with more rows each set reads its half of the rows of every segment (the sums would not fit in registers).
+  static constexpr bool kRowSplit = NT > 16;
+  static constexpr int kEpiRows = kRowSplit ? NT / kEpiSets : NT;     // rows a thread of an epilogue set accumulates
+  static constexpr int kXchBytes = kRowSplit ? 0 : NT * kStripCols * 4;   // the second epilogue set's sums of a slice
+  static_assert(kRing % kEpiSets == 0, "a ring entry always belongs to the same epilogue set");
+  static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kScaleRingBytes + kXchBytes + kNumBars * 8 + 64 + 1024;   // + alignment slack
   static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
@@ -123,15 +140,36 @@ __device__ __forceinline__ int64_t segment_offset(const Geometry& geo, int s, in
   return s < geo.strips4 ? int4_unit_offset(geo, s, 2 * blk) : fp6_unit_offset(geo, s - geo.strips4, 2 * blk);
 }
 
-// Expands one 64-row unit of this thread's column (eight packed words at `su` + lds_lo / lds_hi, plus
-// four two-bit words for FP6) into 32 TMEM columns at a_tmem.
+// Group scales of one segment: nq * 64 bytes behind the packed words of its stage (FP6 and per-channel strips
+// have none).  Offset of the scales inside a stage: INT4 segments fill at most 8192 of the kStageW bytes.
+constexpr uint32_t kStageScaleOff = 8192;
+__device__ __forceinline__ uint32_t segment_scale_bytes(const Geometry& geo, int s) {
+  return (s < geo.strips4 && geo.groups > 1) ? (uint32_t)strip_quads(geo.n4, s) * kQuadCols * 2u : 0u;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
+// Expands one 64-row unit of this thread's column (eight packed words, plus four two-bit words for FP6)
+// into 32 TMEM columns at a_tmem.
 template <bool IS6>
-__device__ __forceinline__ void expand_unit(uint32_t su, uint32_t lds_lo, uint32_t lds_hi, uint32_t two_off, uint32_t a_tmem) {
-  const uint4 lo = lds128(su + lds_lo);          // words 0..3
-  const uint4 hi = lds128(su + lds_hi);          // words 4..7
+__device__ __forceinline__ void expand_words(const uint4& lo, const uint4& hi, const uint4& two, uint32_t a_tmem) {
   const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
   if constexpr (IS6) {
-    const uint4 two = lds128(su + two_off);
     const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
 #pragma unroll
     for (int step = 0; step < 4; ++step) {
@@ -158,7 +196,9 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   // the swizzled activation stages must start on 1024-byte boundaries
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t act_base = smem0 + S * kStageW;
-  const uint32_t bars0 = act_base + R * C::kActBytes;
+  const uint32_t scale_ring = act_base + R * C::kActBytes;      // [entry][column] fp32
+  const uint32_t xch = scale_ring + C::kScaleRingBytes;         // [row][column] fp32
+  const uint32_t bars0 = xch + C::kXchBytes;
   const uint32_t w_full = bars0, w_empty = w_full + 8 * S;
   const uint32_t act_full = w_empty + 8 * S, ready = act_full + 8 * R, done = ready + 8 * R;
   const uint32_t d_free = done + 8 * R;        // the accumulator tile has been read back
@@ -174,6 +214,9 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   const int nseg = B1 - B0;
   FP6M_TRACE_DECL(trace);
   FP6M_TRACE_INIT(trace, cta, warp, lane);
+#ifdef FP6M_TRACE
+  const unsigned long long t_launch = global_ns();
+#endif
   launch_dependents();
   if (nseg <= 0) {                     // no work: still counted, see read_epoch_and_count
     if (tid == 0) {
@@ -182,7 +225,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     }
     return;
   }
-  bool dead = false;
+  WaitState ws;
   const int s_first = B0 / kb, blk_first = B0 - s_first * kb;
   const uint64_t policy = make_evict_first_policy();
 
@@ -193,24 +236,26 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     const int st = warp - C::kDeqBase;
     if (lane == 0) {
       mbar_init(w_full + 8 * st, 1);       // the expect_tx arrival of the weights producer
-      mbar_init(w_empty + 8 * st, 4);      // the four warps of the team that read the stage have their words in registers
+      mbar_init(w_empty + 8 * st, 128);    // every thread of the team that read the stage has used its words
       mbar_fence_init();
       if (st < nseg) {
         int s = s_first, blk = blk_first + st;
         while (blk >= kb) { blk -= kb; ++s; }
-        const uint32_t bytes = segment_bytes(geo, s);
-        mbar_arrive_expect_tx(w_full + 8 * st, bytes);
+        const uint32_t bytes = segment_bytes(geo, s), sbytes = segment_scale_bytes(geo, s);
+        mbar_arrive_expect_tx(w_full + 8 * st, bytes + sbytes);
         tma_load_1d_stream(smem0 + st * kStageW, p.B + segment_offset(geo, s, blk), bytes, w_full + 8 * st, policy);
+        if (sbytes)
+          tma_load_1d_stream(smem0 + st * kStageW + kStageScaleOff, p.S + int4_scale_offset(geo, s, blk), sbytes, w_full + 8 * st, policy);
       }
       FP6M_TRACE_EVENT(trace, 1, st);
     }
   }
   if (tid < 4 * R + 1) {
     const int i = tid;
-    // act_full: expect_tx arrival of the activations producer; ready: the four warps of the segment's team
-    // stored the operands into TMEM; done: the commits of the segment's two issuers; d_free: the four
-    // epilogue warps have read the tile
-    const uint32_t count = i < R ? 1u : (i < 2 * R ? 4u : (i < 3 * R ? 2u : (i < 4 * R ? 4u : 1u)));
+    // act_full: expect_tx arrival of the activations producer; ready: every thread of the segment's team
+    // stored its operands into TMEM; done: the commit(s) of the segment's issuer(s); d_free: every thread of
+    // the entry's epilogue set has read the tile.  (All lanes arrive: no election, no branch.)
+    const uint32_t count = i < R ? 1u : (i < 2 * R ? 128u : (i < 3 * R ? (C::kSplitIssue ? 2u : 1u) : (i < 4 * R ? (C::kRowSplit ? 128u * C::kEpiSets : 128u) : 1u)));
     mbar_init(act_full + 8 * i, count);
     mbar_fence_init();
   }
@@ -254,16 +299,24 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       int s = s_first, blk = blk_first + S;
       while (blk >= kb) { blk -= kb; ++s; }
       const uint8_t* src = p.B + segment_offset(geo, s, blk);
-      uint32_t bytes = segment_bytes(geo, s);
+      uint32_t bytes = segment_bytes(geo, s), sbytes = segment_scale_bytes(geo, s);
+      const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(p.S + (sbytes ? int4_scale_offset(geo, s, blk) : 0));
       int stage = 0;
       uint32_t phase = 0;                      // parity of the stage's previous use
       for (int n = S; n < nseg; ++n) {
-        mbar_wait_bounded<100>(w_empty + 8 * stage, phase, p.status, dead);
-        mbar_arrive_expect_tx(w_full + 8 * stage, bytes);
+        mbar_wait<200>(w_empty + 8 * stage, phase, ws);
+        mbar_arrive_expect_tx(w_full + 8 * stage, bytes + sbytes);
         tma_load_1d_stream(smem0 + stage * kStageW, src, bytes, w_full + 8 * stage, policy);
+        if (sbytes) tma_load_1d_stream(smem0 + stage * kStageW + kStageScaleOff, ssrc, sbytes, w_full + 8 * stage, policy);
         FP6M_TRACE_EVENT(trace, 1, n);
         src += bytes;                          // blocks and strips follow one another without gaps
-        if (++blk == kb) { blk = 0; ++s; bytes = segment_bytes(geo, s); }
+        ssrc += sbytes;                        // and so do the groups of a strip
+        if (++blk == kb) {
+          blk = 0; ++s;
+          bytes = segment_bytes(geo, s);
+          sbytes = segment_scale_bytes(geo, s);
+          if (sbytes) ssrc = reinterpret_cast<const uint8_t*>(p.S + int4_scale_offset(geo, s, 0));
+        }
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
     }
@@ -274,7 +327,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       int r = 0;
       uint32_t phase = 0;                      // parity of the entry's previous use
       for (int n = R; n < nseg; ++n) {
-        mbar_wait_bounded<100>(done + 8 * r, phase, p.status, dead);     // the MMAs that read this tile are done
+        mbar_wait<200>(done + 8 * r, phase, ws);     // the MMAs that read this tile are done
         load_activations(blk, r);
         FP6M_TRACE_EVENT(trace, 5, n);
         if (++blk == kb) blk = 0;
@@ -283,38 +336,62 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     }
   } else if (warp >= 2 && warp < 2 + C::kIssuers) {
     // ================================================================== MMA issuers
-    // Issuer i serves team i / 2 and unit i % 2 of its segments n = team, team + T, ... (ring entry
-    // n % R): four MMAs that add to the tile the team zeroed, then a commit.  The whole warp waits
-    // (warp-uniform control flow); one fixed lane issues the tcgen05 instructions, so that the commit
-    // tracks the MMAs before it.  First of all, issuer i loads the activations of segment i.
+    // Split issue: issuer i serves team i / 2 and unit i % 2 of its segments n = team, team + T, ... (ring
+    // entry n % R): four MMAs that add to the tile the team zeroed, then a commit.  Otherwise issuer r owns
+    // ring entry r and issues all eight MMAs of its segments.  The whole warp waits (warp-uniform control
+    // flow); one fixed lane issues the tcgen05 instructions, so that the commit tracks the MMAs before it.
+    // First of all, issuer i loads the activations of segment i.
     const int mine = warp - 2;
     if (lane == 0 && mine < R && mine < nseg) {
       load_activations((blk_first + mine) % kb, mine);
       FP6M_TRACE_EVENT(trace, 5, mine);
     }
     __syncwarp();
-    const int team = mine >> 1, unit = mine & 1;
-    int r = team;
-    uint32_t rphase = 0;
-    const uint64_t desc0 = wide_act_desc(act_base) + (uint64_t)(unit * (C::kActUnitBytes >> 4));
     constexpr uint32_t kStepDesc = 32 >> 4;            // 16 halves along a 128-byte row
-    for (int n = team; n < nseg; n += T) {
-      mbar_wait_bounded<20>(ready + 8 * r, rphase, p.status, dead);
-      mbar_wait_bounded<20>(act_full + 8 * r, rphase, p.status, dead);
-      tc_fence_after();
-      FP6M_TRACE_EVENT(trace, 6, n);
-      const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
-      const uint32_t a_tmem = tmem + C::kTmemA + r * 64 + unit * 32;
-      // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
-      const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
-      if (lane == 0) {
-        tc_mma_unit<kStepDesc>(d_tmem, a_tmem, desc, C::kIdesc, 1u);
-        tc_commit(done + 8 * r);
+    if constexpr (C::kSplitIssue) {
+      const int team = mine >> 1, unit = mine & 1;
+      int r = team;
+      uint32_t rphase = 0;
+      const uint64_t desc0 = wide_act_desc(act_base) + (uint64_t)(unit * (C::kActUnitBytes >> 4));
+      for (int n = team; n < nseg; n += T) {
+        mbar_wait<32>(ready + 8 * r, rphase, ws);
+        mbar_wait<32>(act_full + 8 * r, rphase, ws);
+        tc_fence_after();
+        FP6M_TRACE_EVENT(trace, 6, n);
+        const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
+        const uint32_t a_tmem = tmem + C::kTmemA + r * 64 + unit * 32;
+        // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
+        const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
+        if (lane == 0) {
+          tc_mma_unit<kStepDesc>(d_tmem, a_tmem, desc, C::kIdesc, 1u);
+          tc_commit(done + 8 * r);
+        }
+        __syncwarp();
+        FP6M_TRACE_EVENT(trace, 7, n);
+        r += T;
+        if (r >= R) { r -= R; rphase ^= 1; }
       }
-      __syncwarp();
-      FP6M_TRACE_EVENT(trace, 7, n);
-      r += T;
-      if (r >= R) { r -= R; rphase ^= 1; }
+    } else {
+      // issuer r owns ring entry r: the segments n = r, r + R, ...; the first MMA overwrites the tile
+      const int r = mine;
+      uint32_t rphase = 0;
+      const uint64_t desc = wide_act_desc(act_base) + (uint64_t)(r * (C::kActBytes >> 4));
+      const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
+      const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
+      for (int n = r; n < nseg; n += R) {
+        mbar_wait<32>(ready + 8 * r, rphase, ws);
+        mbar_wait<32>(act_full + 8 * r, rphase, ws);
+        tc_fence_after();
+        FP6M_TRACE_EVENT(trace, 6, n);
+        if (lane == 0) {
+          tc_mma_unit<kStepDesc>(d_tmem, a_tmem, desc, C::kIdesc, 0u);
+          tc_mma_unit<kStepDesc>(d_tmem, a_tmem + 32, desc + (C::kActUnitBytes >> 4), C::kIdesc, 1u);
+          tc_commit(done + 8 * r);
+        }
+        __syncwarp();
+        FP6M_TRACE_EVENT(trace, 7, n);
+        rphase ^= 1;
+      }
     }
   } else if (warp >= C::kDeqBase && warp < C::kEpiBase) {
     // ================================================================== dequantisers
@@ -328,50 +405,99 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16
     const uint32_t lds_hi = lds_lo ^ 16;
 
-    int n = team, stage = team, r = team;
-    uint32_t wphase = 0, rphase = 1;                 // rphase: parity of the entry's previous use (a fresh barrier passes parity 1)
-    // the team's segments of one strip: n, n + T, ... < n_end
-    auto run_strip = [&](auto is6_tag, int nq, int n_end) {
-      constexpr bool IS6 = decltype(is6_tag)::value;
-      const uint32_t unit_bytes = nq * (IS6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
-      const uint32_t two_off = nq * kInt4UnitQuadBytes + c * 16;
-#pragma unroll 1
-      for (; n < n_end; n += T) {
-        FP6M_TRACE_EVENT(trace, 10, n);
-        mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
-        FP6M_TRACE_EVENT(trace, 11, n);
-        // the MMAs that read this operand slot R segments ago have finished, and the epilogue has read their sums
-        mbar_wait_bounded(done + 8 * r, rphase, p.status, dead);
-        mbar_wait_bounded(d_free + 8 * r, rphase, p.status, dead);
-        tc_fence_after();
-        FP6M_TRACE_EVENT(trace, 12, n);
-        // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
-        const uint32_t st = smem0 + stage * kStageW;
-        const uint32_t a_tmem = a_base + r * 64;
-        tc_st_zero<NT>(d_base + r * NT);              // the issuers' MMAs all accumulate
-        expand_unit<IS6>(st, lds_lo, lds_hi, two_off, a_tmem);
-        expand_unit<IS6>(st + unit_bytes, lds_lo, lds_hi, two_off, a_tmem + 32);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
-        tc_wait_st();
-        tc_fence_before();
-        if (lane == 0) mbar_arrive(ready + 8 * r);
-        FP6M_TRACE_EVENT(trace, 13, n);
-        stage += T;
-        if (stage >= S) { stage -= S; wphase ^= 1; }
-        r += T;
-        if (r >= R) { r -= R; rphase ^= 1; }
-      }
+    // The packed words of a segment are loaded one iteration ahead: while the TMEM stores of segment n drain,
+    // the team already waits for and loads segment n + T.
+    struct Words {
+      uint4 lo0, hi0, lo1, hi1;      // unit 0 and unit 1: words 0..3, 4..7 of this thread's column
+      uint4 two0, two1;              // FP6: the two-bit words of the units
+      uint32_t scale_raw;            // fp16 bits of the column's group scale (1.0 where the strip has none)
     };
-    for (int s = s_first; n < nseg; ++s) {
-      const int n_end = min(nseg, (s + 1) * kb - B0);       // first segment of the next strip
-      if (s < geo.strips4) run_strip(std::false_type{}, strip_quads(geo.n4, s), n_end);
-      else run_strip(std::true_type{}, strip_quads(geo.n6, s - geo.strips4), n_end);
+    struct Strip {
+      int n_end;                     // first segment (of the CTA) beyond the strip
+      bool is6, scaled;
+      uint32_t unit_bytes, two_off;
+    };
+    auto open_strip = [&](int s) {
+      Strip sp;
+      sp.n_end = min(nseg, (s + 1) * kb - B0);
+      sp.is6 = s >= geo.strips4;
+      const int nq = sp.is6 ? strip_quads(geo.n6, s - geo.strips4) : strip_quads(geo.n4, s);
+      sp.unit_bytes = nq * (sp.is6 ? kFp6UnitQuadBytes : kInt4UnitQuadBytes);
+      sp.two_off = nq * kInt4UnitQuadBytes + c * 16;
+      sp.scaled = !sp.is6 && geo.groups > 1;       // the group scales came with the packed words
+      return sp;
+    };
+    // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
+    auto load_words = [&](const Strip& sp, int stage, Words& w) {
+      const uint32_t st = smem0 + stage * kStageW;
+      w.lo0 = lds128(st + lds_lo);
+      w.hi0 = lds128(st + lds_hi);
+      w.lo1 = lds128(st + sp.unit_bytes + lds_lo);
+      w.hi1 = lds128(st + sp.unit_bytes + lds_hi);
+      if (sp.is6) {
+        w.two0 = lds128(st + sp.two_off);
+        w.two1 = lds128(st + sp.unit_bytes + sp.two_off);
+      }
+      w.scale_raw = sp.scaled ? lds_u16(st + kStageScaleOff + 2 * c) : 0x3C00u;
+    };
+
+    int n = team, stage = team, r = team, s = s_first;
+    uint32_t wphase = 0, rphase = 1;                 // rphase: parity of the entry's previous use (a fresh barrier passes parity 1)
+    Strip sp = open_strip(s);
+    while (n >= sp.n_end && sp.n_end < nseg) sp = open_strip(++s);
+    Words w;
+    if (n < nseg) {
+      mbar_wait(w_full + 8 * stage, wphase, ws);
+      load_words(sp, stage, w);
+    }
+#pragma unroll 1
+    while (n < nseg) {
+      FP6M_TRACE_EVENT(trace, 10, n);
+      // the epilogue has read the sums of the segment that used this ring entry before (so its MMAs are done too)
+      mbar_wait(d_free + 8 * r, rphase, ws);
+      tc_fence_after();
+      FP6M_TRACE_EVENT(trace, 12, n);
+      const uint32_t a_tmem = a_base + r * 64;
+      // this column's scale of the block goes on to the epilogue warps
+      sts_u32(scale_ring + (r * kStripCols + c) * 4, w.scale_raw);
+      if constexpr (C::kSplitIssue) tc_st_zero<NT>(d_base + r * NT);       // both issuers' MMAs accumulate
+      if (sp.is6) {
+        expand_words<true>(w.lo0, w.hi0, w.two0, a_tmem);
+        expand_words<true>(w.lo1, w.hi1, w.two1, a_tmem + 32);
+      } else {
+        expand_words<false>(w.lo0, w.hi0, w.two0, a_tmem);
+        expand_words<false>(w.lo1, w.hi1, w.two1, a_tmem + 32);
+      }
+      FP6M_TRACE_EVENT(trace, 17, n);
+      mbar_arrive(w_empty + 8 * stage);                         // this thread has used its words of the stage
+      // the team's next segment: wait for it and load its words while the stores above drain
+      const int n_next = n + T;
+      stage += T;
+      if (stage >= S) { stage -= S; wphase ^= 1; }
+      bool was6 = sp.is6;
+      while (n_next >= sp.n_end && sp.n_end < nseg) sp = open_strip(++s);
+      if (n_next < nseg) {
+        mbar_wait(w_full + 8 * stage, wphase, ws);
+        load_words(sp, stage, w);
+      }
+      (void)was6;
+      FP6M_TRACE_EVENT(trace, 18, n);
+      tc_wait_st();
+      FP6M_TRACE_EVENT(trace, 19, n);
+      tc_fence_before();
+      mbar_arrive(ready + 8 * r);
+      FP6M_TRACE_EVENT(trace, 13, n);
+      r += T;
+      if (r >= R) { r -= R; rphase ^= 1; }
+      n = n_next;
     }
   } else if (warp >= C::kEpiBase) {
     // ================================================================== epilogue
-    // One warp per lane quarter; thread = weight column.  Reads every segment's accumulator tile back,
-    // scales, accumulates; writes a slice out when its last segment has been added.
+    // Two sets of one warp per lane quarter; thread = weight column.  Set e reads the accumulator tiles of
+    // the segments n = e, e + 2, ... back, scales and accumulates; at the end of a slice set 1 passes its
+    // sums to set 0, which writes the slice out (sums added in the order set 0 + set 1: fixed).
+    constexpr int kEpiThreads = 128 * C::kEpiSets;
+    const int eset = (warp - C::kEpiBase) >> 2;
     const int quarter = warp & 3;
     const int c = quarter * 32 + lane;
     const uint32_t d_base = tmem + ((uint32_t)(quarter * 32) << 16) + C::kTmemD;       // + r * NT
@@ -414,123 +540,186 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       const int cc_first = (p.sched.bound[cc] >> 1) / kb;
       return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
     };
+    constexpr int ROWS = C::kEpiRows;
+    const int row0 = C::kRowSplit ? eset * ROWS : 0;          // this set's rows of A and C (all of them when the sets take turns)
     int reduce_strip = -1;                           // strip this CTA must reduce at its end
     uint32_t reduce_tag = 0;
-    auto write_strip = [&](const Slice& sl, const float (&v)[NT]) {
+    auto write_strip = [&](const Slice& sl, const float (&v)[ROWS]) {
       const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
       const bool writes = c < ncols;
       const float col_scale = column_scale(sl, writes);
-      if (writes) {
+      float out[ROWS];
 #pragma unroll
-        for (int m = 0; m < NT; ++m)
-          if (m < p.M) store_result(p, m, sl.is6, sl.strip * kStripCols + c, v[m] * col_scale);
-      }
+      for (int m = 0; m < ROWS; ++m) out[m] = v[m] * col_scale;
+      store_column_rows<ROWS>(p, row0, sl.is6, sl.strip * kStripCols + c, out, writes);
     };
-    auto finish_slice = [&](const Slice& sl, const float (&out)[NT]) {
+    auto finish_slice = [&](const Slice& sl, const float (&out)[ROWS]) {
       if (sl.b0 == 0 && sl.b1 == kb) {               // the whole strip was ours
         write_strip(sl, out);
         return;
       }
-      mbar_wait_bounded(epoch_bar, 0, p.status, dead);   // completed long ago: orders the read of misc[1]
+      mbar_wait(epoch_bar, 0, ws);   // completed long ago: orders the read of misc[1]
       const uint32_t tag = misc[1] + 1;
-      unsigned long long* slot = slot_of(cta, sl.strip_lin);
+      unsigned long long* slot = slot_of(cta, sl.strip_lin) + row0 * kStripCols;
 #pragma unroll
-      for (int m = 0; m < NT; ++m)
+      for (int m = 0; m < ROWS; ++m)
         st_relaxed_u64(slot + m * kStripCols, ((unsigned long long)tag << 32) | __float_as_uint(out[m]));
       if (sl.b1 == kb) {                             // last contributor of the strip: reduce it at the end
         reduce_strip = sl.strip_lin;
         reduce_tag = tag;
       }
     };
+    // After the last slice: the strip whose last contributor this CTA is.  Both epilogue sets take part, each
+    // with its share of the rows; sixteen tagged words travel together per thread (two contributors at a time
+    // for eight rows), and a value is added in CTA order, so the sum does not depend on the timing.
     auto finish_cta = [&]() {
       if (reduce_strip < 0) return;
+      constexpr int RR = C::kRowSplit ? ROWS : NT / C::kEpiSets;      // rows this thread reduces
+      const int rr0 = C::kRowSplit ? row0 : eset * RR;
+      constexpr int kChunk = RR < 16 ? RR : 16;                       // rows per round
+      constexpr int kBatch = 16 / kChunk;                             // contributors per round: 16 tagged words in flight per thread
       const Slice sl = open_slice(reduce_strip, 0, kb);
       const int s_begin = reduce_strip * kb;         // first block of the strip
       int c_lo = cta;
       while (c_lo > 0 && (p.sched.bound[c_lo] >> 1) > s_begin) --c_lo;
-      float sum[NT];
+      float sum[RR];
 #pragma unroll
-      for (int m = 0; m < NT; ++m) sum[m] = 0.f;
-      for (int cc = c_lo; cc <= cta; ++cc) {
-        if (p.sched.bound[cc] >= p.sched.bound[cc + 1]) continue;       // a CTA without work stored nothing
-        const unsigned long long* src = slot_of(cc, reduce_strip);
-        unsigned long long v[NT];
-        bool all_here = false;
+      for (int m = 0; m < RR; ++m) sum[m] = 0.f;
 #pragma unroll 1
-        for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
+      for (int cbase = c_lo; cbase <= cta; cbase += kBatch) {
+        bool live[kBatch];
+        const unsigned long long* src[kBatch];
 #pragma unroll
-          for (int m = 0; m < NT; ++m) v[m] = ld_relaxed_u64(src + m * kStripCols);
-          all_here = true;
-#pragma unroll
-          for (int m = 0; m < NT; ++m) all_here = all_here && (uint32_t)(v[m] >> 32) == reduce_tag;
-          if (dead) break;
-        }
-        if (!all_here && !dead) {
-          dead = true;
-          if (p.status) atomicExch(p.status, kStatusTimeout);
+        for (int i = 0; i < kBatch; ++i) {
+          const int cc = cbase + i;
+          live[i] = cc <= cta && p.sched.bound[cc] < p.sched.bound[cc + 1];       // a CTA without work stored nothing
+          src[i] = slot_of(live[i] ? cc : cta, reduce_strip) + rr0 * kStripCols;
         }
 #pragma unroll
-        for (int m = 0; m < NT; ++m) sum[m] += __uint_as_float((uint32_t)v[m]);
+        for (int m0 = 0; m0 < RR; m0 += kChunk) {
+          unsigned long long v[kBatch][kChunk];
+          bool all_here = false;
+#pragma unroll 1
+          for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+              for (int m = 0; m < kChunk; ++m) v[i][m] = ld_relaxed_u64(src[i] + (m0 + m) * kStripCols);
+            all_here = true;
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+              for (int m = 0; m < kChunk; ++m) all_here = all_here && (!live[i] || (uint32_t)(v[i][m] >> 32) == reduce_tag);
+            if (ws.failed) break;                       // a wait of this thread ran out before: do not wait again
+          }
+          if (!all_here) ws.failed = 1;
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+            for (int m = 0; m < kChunk; ++m) sum[m0 + m] += live[i] ? __uint_as_float((uint32_t)v[i][m]) : 0.f;
+        }
       }
-      write_strip(sl, sum);
+      const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      const bool writes = c < ncols;
+      const float col_scale = column_scale(sl, writes);
+#pragma unroll
+      for (int m = 0; m < RR; ++m) sum[m] *= col_scale;
+      store_column_rows<RR>(p, rr0, sl.is6, sl.strip * kStripCols + c, sum, writes);
     };
 
-    float acc[NT];
+    float acc[ROWS];
 #pragma unroll
-    for (int m = 0; m < NT; ++m) acc[m] = 0.f;
-    int n = 0, r = 0;
+    for (int m = 0; m < ROWS; ++m) acc[m] = 0.f;
+    constexpr int kStep = C::kRowSplit ? 1 : C::kEpiSets;      // segments from one of this set's to its next
+    if (!C::kRowSplit && eset == 0) named_bar_arrive(2, kEpiThreads);       // the exchange buffer starts out free
+    int n = C::kRowSplit ? 0 : eset, r = n, n_first = 0;    // n_first: first segment of the current slice
     uint32_t rphase = 0;
-    for (int s = s_first; n < nseg; ++s) {
+    for (int s = s_first; n_first < nseg; ++s) {
       const int b0 = s == s_first ? blk_first : 0;
       const int n_end = min(nseg, (s + 1) * kb - B0);
-      const Slice sl = open_slice(s, b0, b0 + (n_end - n));
-      const int nq = strip_quads(sl.is6 ? geo.n6 : geo.n4, sl.strip);
-      const bool scaled = sl.group && c < nq * kQuadCols;      // padded quads of a ragged strip hold no scales
-      const int scale_stride = nq * kQuadCols;
-      const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.S) +
-                                 (scaled ? int4_scale_offset(geo, sl.strip, 0) + c + (size_t)b0 * scale_stride : 0);
-      unsigned short scale_raw = scaled ? __ldg(sp) : (unsigned short)0x3C00;     // 1.0 unless the strip has group scales
+      const Slice sl = open_slice(s, b0, b0 + (n_end - n_first));
 #pragma unroll 1
-      for (; n < n_end; ++n) {
-        const float scale = __half2float(__ushort_as_half(scale_raw));
-        sp += scale_stride;
-        if (scaled && n + 1 < n_end) scale_raw = __ldg(sp);      // the next block's scale travels during this one
-        mbar_wait_bounded(done + 8 * r, rphase, p.status, dead);
+      for (; n < n_end; n += kStep) {
+        // the team's arrival on `ready` published the column scales of this entry
+        mbar_wait(ready + 8 * r, rphase, ws);
+        const float scale = __half2float(__ushort_as_half((unsigned short)lds_u32(scale_ring + (r * kStripCols + c) * 4)));
+        mbar_wait(done + 8 * r, rphase, ws);
         tc_fence_after();
         FP6M_TRACE_EVENT(trace, 15, n);
-        float d[NT];
 #pragma unroll
-        for (int m0 = 0; m0 < NT; m0 += 16) tc_ld16(d_base + r * NT + m0, *reinterpret_cast<float(*)[16]>(d + m0));
+        for (int m0 = 0; m0 < ROWS; m0 += 16) {
+          float d[16];
+          tc_ld16(d_base + r * NT + row0 + m0, d);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[m0 + i] = fmaf(scale, d[i], acc[m0 + i]);
+        }
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(d_free + 8 * r);     // the team may zero the tile for its next segment
-#pragma unroll
-        for (int m = 0; m < NT; ++m) acc[m] = fmaf(scale, d[m], acc[m]);
+        mbar_arrive(d_free + 8 * r);                    // the team may zero the tile for its next segment
         FP6M_TRACE_EVENT(trace, 16, n);
-        if (++r == R) { r = 0; rphase ^= 1; }
+        r += kStep;
+        if (r >= R) { r -= R; rphase ^= 1; }
       }
+      n_first = n_end;
       FP6M_TRACE_EVENT(trace, 20, s);
-      finish_slice(sl, acc);
+      if constexpr (C::kRowSplit) {
+        finish_slice(sl, acc);
+      } else if (eset == 1) {
+        // set 0 has read the previous slice's sums out of the exchange buffer (barrier 2); publish (barrier 1)
+        named_bar_sync(2, kEpiThreads);
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) sts_f32(xch + (m * kStripCols + c) * 4, acc[m]);
+        named_bar_arrive(1, kEpiThreads);
+        if (!(sl.b0 == 0 && sl.b1 == kb) && sl.b1 == kb) {      // as set 0 finds in finish_slice: this CTA reduces the strip
+          mbar_wait(epoch_bar, 0, ws);
+          reduce_strip = sl.strip_lin;
+          reduce_tag = misc[1] + 1;
+        }
+      } else {
+        named_bar_sync(1, kEpiThreads);
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) acc[m] += lds_f32(xch + (m * kStripCols + c) * 4);
+        named_bar_arrive(2, kEpiThreads);
+        finish_slice(sl, acc);
+      }
       FP6M_TRACE_EVENT(trace, 22, s);
 #pragma unroll
-      for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+      for (int m = 0; m < ROWS; ++m) acc[m] = 0.f;
     }
     finish_cta();
     FP6M_TRACE_EVENT(trace, 23, 0);
   }
 
+  report_waits(ws, p.status);
   // ---- all roles are done with tensor memory: give it back
   tc_fence_before();
   __syncthreads();
   FP6M_TRACE_EVENT(trace, 24, 0);
+#ifdef FP6M_TRACE
+  if (tid == 0 && cta < 160) {
+    g_launch_times[misc[1] & 63][cta][0] = t_launch;
+    g_launch_times[misc[1] & 63][cta][1] = global_ns();
+  }
+#endif
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
   }
 }
 
-using Tc5Rows16 = Tc5Cfg<16, 15, 6, 3>;     // 6 x 16 + 6 x 64 = 480 TMEM columns
+#ifndef FP6M_TC5_TEAMS
+#define FP6M_TC5_TEAMS 3
+#define FP6M_TC5_STAGES 15
+#endif
+using Tc5Rows16 = Tc5Cfg<16, FP6M_TC5_STAGES, 2 * FP6M_TC5_TEAMS, FP6M_TC5_TEAMS, true>;          // 3 teams: 6 x 16 + 6 x 64 = 480 TMEM columns
+using Tc5Rows16Ordered = Tc5Cfg<16, FP6M_TC5_STAGES, 2 * FP6M_TC5_TEAMS, FP6M_TC5_TEAMS, false>;  // one issuing thread per accumulator tile: run-to-run bit-identical
+// 17 to 64 rows: two teams, four ring entries (4 x 64 + 4 x 32 = 384, 4 x 64 + 4 x 64 = 512 TMEM columns); the
+// activation tiles grow with the rows, the weight stages give way
+using Tc5Rows32 = Tc5Cfg<32, 14, 4, 2, true>;
+using Tc5Rows32Ordered = Tc5Cfg<32, 14, 4, 2, false>;
+using Tc5Rows64 = Tc5Cfg<64, 10, 4, 2, true>;
+using Tc5Rows64Ordered = Tc5Cfg<64, 10, 4, 2, false>;
 
 bool g_overlap_launches = false;
+bool g_ordered_sums = false;
 
 template <class C>
 cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
@@ -563,6 +752,10 @@ cudaError_t launch_tc5(const MulParams& p, cudaStream_t stream) {
 }  // namespace
 
 #ifdef FP6M_TRACE
+extern "C" int fp6m_launch_times_read(unsigned long long* out, size_t bytes) {
+  if (bytes < sizeof(g_launch_times)) return -1;
+  return (int)cudaMemcpyFromSymbol(out, g_launch_times, sizeof(g_launch_times));
+}
 extern "C" int fp6m_trace_read(unsigned long long* out, size_t bytes) {
   if (bytes < sizeof(g_trace)) return -1;
   return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
@@ -570,18 +763,27 @@ extern "C" int fp6m_trace_read(unsigned long long* out, size_t bytes) {
 #endif
 
 void tc5_set_overlap(bool on) { g_overlap_launches = on; }
+void tc5_set_ordered_sums(bool on) { g_ordered_sums = on; }
+bool tc5_get_ordered_sums() { return g_ordered_sums; }
 bool tc5_get_overlap() { return g_overlap_launches; }
 
 // CTAs per SM the kernel is sized for, for `rows` rows of A in one pass.
 int tc5_ctas_per_sm(int rows) { (void)rows; return 1; }
 
+// rows of the MMA tile used for `rows` (<= 64) rows of A
+int tc5_tile_rows(int rows) { return rows <= 16 ? 16 : (rows <= 32 ? 32 : 64); }
+
 size_t tc5_scratch_bytes(int ctas, int rows) {
-  (void)rows;
-  const int nt = 16;
-  return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * nt * kStripCols * sizeof(unsigned long long);
+  return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * tc5_tile_rows(rows) * kStripCols * sizeof(unsigned long long);
 }
 
-// Runs the GEMM for rows [0, p.M) with p.M <= 16.  The schedule's unit boundaries must be even (whole blocks).
-cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream) { return launch_tc5<Tc5Rows16>(p, stream); }
+// Runs the GEMM for rows [0, p.M) with p.M <= 64.  The schedule's unit boundaries must be even (whole blocks).
+cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream) {
+  switch (tc5_tile_rows(p.M)) {
+    case 16: return g_ordered_sums ? launch_tc5<Tc5Rows16Ordered>(p, stream) : launch_tc5<Tc5Rows16>(p, stream);
+    case 32: return g_ordered_sums ? launch_tc5<Tc5Rows32Ordered>(p, stream) : launch_tc5<Tc5Rows32>(p, stream);
+    default: return g_ordered_sums ? launch_tc5<Tc5Rows64Ordered>(p, stream) : launch_tc5<Tc5Rows64>(p, stream);
+  }
+}
 
 }  // namespace fp6m

@@ -1,8 +1,8 @@
-// W(4&6)A16 GEMM on tcgen05 + TMEM for 17 to 256 rows of A per pass.
+// W(4&6)A16 GEMM on tcgen05 + TMEM for 65 to 256 rows of A per pass (up to 64 rows: gemm_tc5.cu).
 //
 // As in the kernel for up to 16 rows (gemm_tc5.cu) the product is computed transposed: the 128 weight
 // columns of a strip are the M dimension of tcgen05.mma (one TMEM lane per column), the rows of A its
-// N dimension (32 ... 256), the dequantised weights the A operand in TENSOR MEMORY.  Differences:
+// N dimension (128 or 256), the dequantised weights the A operand in TENSOR MEMORY.  Differences:
 //   * The INT4 group scale is multiplied into the operand - fp16(q - 8) * s_g with one fp16 rounding,
 //     bit for bit the dequantised weight of the reference's rule (test.py:98) - so ONE accumulator
 //     tile collects a whole slice of K and is read back once per slice, not once per scale group.
@@ -56,7 +56,7 @@ struct WideCfg {
   static constexpr int kRowsPerTeam = NT / kTeams;     // rows of the accumulator tile a team writes out
   static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   static constexpr int kChunk = kRowsPerTeam < 16 ? kRowsPerTeam : 16;   // rows read back per tcgen05.ld
-  static_assert(kTmemUsed <= 512 && (kRowsPerTeam % 16 == 0 || kRowsPerTeam == 8) && kStages >= kTeams && kRing >= kTeams, "configuration");
+  static_assert(kTmemUsed <= 512 && (kRowsPerTeam % 16 == 0 || kRowsPerTeam == 8) && kStages >= kTeams && kRing % kTeams == 0, "configuration");
 };
 
 // coordinates {k0, row0}: k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
@@ -286,12 +286,10 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotWords + row0 * kStripCols + c;
     };
     auto store_rows = [&](const Slice& sl, int m0, const float (&v)[CH], float col_scale, bool writes) {
-      if (writes) {
+      float out[CH];
 #pragma unroll
-        for (int i = 0; i < CH; ++i)
-          if (sl.tile_row0 + row0 + m0 + i < p.M)
-            store_result(p, sl.tile_row0 + row0 + m0 + i, sl.is6, sl.strip * kStripCols + c, v[i] * col_scale);
-      }
+      for (int i = 0; i < CH; ++i) out[i] = v[i] * col_scale;
+      store_column_rows<CH>(p, sl.tile_row0 + row0 + m0, sl.is6, sl.strip * kStripCols + c, out, writes);
     };
 
     int reduce_strip = -1;                           // strip this CTA must reduce at its end
@@ -465,10 +463,10 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   }
 }
 
-using Wide32 = WideCfg<32, 4, 4, 8, 8, 6>;      // 4 x 32 + 6 x 64 = 512 TMEM columns
-using Wide64 = WideCfg<64, 4, 4, 8, 8, 4>;      // 4 x 64 + 4 x 64
-using Wide128 = WideCfg<128, 2, 2, 6, 6, 4>;    // 2 x 128 + 4 x 64
-using Wide256 = WideCfg<256, 2, 1, 4, 4, 3>;    // 256 + 3 x 64
+// The number of operand slots is a multiple of the number of teams, so a slot always belongs to the same team
+// and every waiter of a barrier sees each of its phases (a parity wait that skipped a phase would pass early).
+using Wide128 = WideCfg<128, 2, 2, 6, 6, 4>;    // 2 x 128 + 4 x 64 = 512 TMEM columns
+using Wide256 = WideCfg<256, 2, 1, 4, 4, 4>;    // 256 + 4 x 64
 
 template <class C>
 cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
@@ -518,9 +516,40 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 
+// The last few tensor maps of the calling thread: a decode loop calls with the same activation buffer again
+// and again, and encoding a map costs a driver call.  (A map depends on the pointer and the shape only.)
+namespace {
+struct MapKey {
+  const void* A;
+  int M, K, box_rows, dims;
+};
+struct MapCache {
+  static constexpr int kEntries = 8;
+  MapKey key[kEntries] = {};
+  CUtensorMap map[kEntries];
+  int next = 0;
+  bool find(const MapKey& k, CUtensorMap* out) const {
+    for (int i = 0; i < kEntries; ++i)
+      if (key[i].A == k.A && key[i].M == k.M && key[i].K == k.K && key[i].box_rows == k.box_rows && key[i].dims == k.dims) {
+        *out = map[i];
+        return true;
+      }
+    return false;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    key[next] = k;
+    map[next] = m;
+    next = (next + 1) % kEntries;
+  }
+};
+thread_local MapCache g_map_cache;
+}  // namespace
+
 // A as a K x M tensor (K contiguous): one box = 64 halves x `box_rows` rows = the activations of one
 // 64-row unit, written to shared memory with the 128-byte swizzle; rows beyond M read as zero.
 cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUtensorMap* map) {
+  const MapKey mk = {A, M, K, box_rows, 2};
+  if (g_map_cache.find(mk, map)) return cudaSuccess;
   EncodeTiledFn encode = encode_tiled();
   if (!encode) return cudaErrorNotSupported;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
@@ -530,6 +559,7 @@ cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUt
   if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
+  g_map_cache.put(mk, *map);
   return cudaSuccess;
 }
 
@@ -537,6 +567,8 @@ cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUt
 // activations of one 128-row block as two swizzled tiles, one behind the other; units beyond K and rows
 // beyond M read as zero.
 cudaError_t encode_activation_segment_map(const half* A, int M, int K, int box_rows, CUtensorMap* map) {
+  const MapKey mk = {A, M, K, box_rows, 3};
+  if (g_map_cache.find(mk, map)) return cudaSuccess;
   EncodeTiledFn encode = encode_tiled();
   if (!encode) return cudaErrorNotSupported;
   const cuuint64_t dims[3] = {64, (cuuint64_t)M, (cuuint64_t)(K / 64)};
@@ -546,13 +578,14 @@ cudaError_t encode_activation_segment_map(const half* A, int M, int K, int box_r
   if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<half*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
+  g_map_cache.put(mk, *map);
   return cudaSuccess;
 }
 
 int wide_rows_per_pass() { return 256; }   // the widest tile
 
 // rows of the MMA tile used for `rows` rows of A
-int wide_tile_rows(int rows) { return rows <= 32 ? 32 : (rows <= 64 ? 64 : (rows <= 128 ? 128 : 256)); }
+int wide_tile_rows(int rows) { return rows <= 128 ? 128 : 256; }
 
 size_t wide_scratch_bytes(int ctas, int rows) {
   return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * wide_tile_rows(rows) * kStripCols * sizeof(unsigned long long);
@@ -561,12 +594,7 @@ size_t wide_scratch_bytes(int ctas, int rows) {
 // Runs the GEMM for rows [0, p.M) in p.row_tiles tiles of `tile_rows` rows; the host dispatcher loops over larger M.
 cudaError_t launch_gemm_wide(const MulParams& p, int tile_rows, cudaStream_t stream) {
   const bool overlap = tc5_get_overlap();
-  switch (tile_rows) {
-    case 32: return launch_wide<Wide32>(p, stream, overlap);
-    case 64: return launch_wide<Wide64>(p, stream, overlap);
-    case 128: return launch_wide<Wide128>(p, stream, overlap);
-    default: return launch_wide<Wide256>(p, stream, overlap);
-  }
+  return tile_rows <= 128 ? launch_wide<Wide128>(p, stream, overlap) : launch_wide<Wide256>(p, stream, overlap);
 }
 
 }  // namespace fp6m

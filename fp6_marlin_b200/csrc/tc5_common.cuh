@@ -126,6 +126,42 @@ __device__ __forceinline__ void store_result(const Params& p, int row, bool is6,
   }
 }
 
+// Stores kRows finished values of one weight column (this thread's; neighbouring lanes hold neighbouring
+// columns), rows row0 .. row0 + kRows - 1, applying the epilogue: v[i] is the fp32 sum times the column scale.
+// Every lane of the warp must call it (the gate / up pairs are exchanged between lanes); `writes` says
+// whether the column exists.  The epilogues extend the reference's write_result
+// (fp6_marlin_cuda_kernel.cu:698-749), which only scales and stores.
+template <int kRows, class Params>
+__device__ __forceinline__ void store_column_rows(const Params& p, int row0, bool is6, int col, const float (&v)[kRows], bool writes) {
+  if (p.epilogue == kEpilogueSiluMul) {
+    const int half_n = p.N >> 1;
+    const size_t out_col = (size_t)((is6 ? p.geo.n4 : 0) + col) >> 1;
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const float up = __shfl_xor_sync(0xffffffffu, v[i], 1);          // the odd neighbour's value
+      if (writes && (col & 1) == 0 && row0 + i < p.M) {
+        const float g = v[i];
+        p.C[(size_t)(row0 + i) * half_n + out_col] = __float2half_rn(g / (1.f + __expf(-g)) * up);
+      }
+    }
+    return;
+  }
+  if (!writes) return;
+  if (p.epilogue == kEpilogueResidual) {
+    const size_t at = (size_t)(is6 ? p.geo.n4 : 0) + col;
+#pragma unroll
+    for (int i = 0; i < kRows; ++i)
+      if (row0 + i < p.M) {
+        const size_t idx = (size_t)(row0 + i) * p.N + at;
+        p.C[idx] = __float2half_rn(v[i] + __half2float(p.R[idx]));
+      }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < kRows; ++i)
+    if (row0 + i < p.M) store_result(p, row0 + i, is6, col, v[i]);
+}
+
 // ---- activations by tiled TMA --------------------------------------------------------------------
 // activations of one unit: K-major, 128-byte swizzle (layout type 2), 1024 bytes between 8-row groups;
 // the leading-dimension field is not used by swizzled K-major layouts

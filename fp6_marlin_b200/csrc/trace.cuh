@@ -14,6 +14,14 @@ constexpr int kTraceEntries = 1024;
 __device__ const int kTraceCtas[kTraceCtaCount] = {0, 97};
 __device__ unsigned long long g_trace[kTraceCtaCount][kTraceWarps][kTraceEntries];
 
+// start / end of every CTA of the last 64 launches in nanoseconds (%globaltimer), indexed by launch epoch
+__device__ unsigned long long g_launch_times[64][160][2];
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 struct Tracer {
   unsigned long long* buf;
   long long t0;

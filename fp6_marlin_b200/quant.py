@@ -147,3 +147,28 @@ def select_outlier_columns(w: torch.Tensor, quant_cols: int) -> torch.Tensor:
     mask = torch.ones(n, dtype=torch.bool, device=w.device)
     mask[outliers] = False
     return torch.cat([torch.arange(n, device=w.device)[mask], outliers])
+
+
+def make_gate_up_weight(w_gate: torch.Tensor, w_up: torch.Tensor, quant_cols: int = 256, group_size: int = 128,
+                        keep_dequantized: bool = False, quant_device=None):
+    """Gate and up projections W_gate[k, i], W_up[k, i] (fp16) -> one packed weight of 2i columns for
+    ``mul_fused(..., epilogue="silu_mul")``, plus the order of the outputs.
+
+    Pairs stay together: the ``quant_cols / 2`` pairs (gate_j, up_j) whose larger abs-max is largest become
+    FP6 (ties toward the lower j), the others INT4; inside each region the columns alternate gate_j, up_j, in
+    increasing j.  Returns ``(weight, order)`` where output column t of the fused GEMM is
+    ``silu(x @ W_gate[:, order[t]]) * (x @ W_up[:, order[t]])``.
+    """
+    assert w_gate.shape == w_up.shape and w_gate.dtype == torch.float16 and w_up.dtype == torch.float16
+    k, inter = w_gate.shape
+    qc = max(quant_cols, 0)
+    assert qc % 2 == 0 and qc // 2 <= inter
+    score = torch.maximum(torch.amax(torch.abs(w_gate.float()), dim=0), torch.amax(torch.abs(w_up.float()), dim=0))
+    ranked = torch.sort(score, descending=True, stable=True)[1]
+    outliers = torch.sort(ranked[: qc // 2])[0]
+    mask = torch.ones(inter, dtype=torch.bool, device=w_gate.device)
+    mask[outliers] = False
+    order = torch.cat([torch.arange(inter, device=w_gate.device)[mask], outliers])
+    w = torch.stack([w_gate[:, order], w_up[:, order]], dim=2).reshape(k, 2 * inter).contiguous()
+    weight = make_w46_weight(w, quant_cols if qc else -1, group_size, keep_dequantized, quant_device)
+    return weight, order

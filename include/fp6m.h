@@ -112,6 +112,20 @@ int fp6m_mul(const void* A, const void* B, void* C, const void* s, int M, int N,
              int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
              int quant_cols, int group_size, int layout, int* status_dev);
 
+/* fp6m_mul with the step that follows the GEMM in a transformer block fused into its epilogue, on the fp32
+ * sums before the one rounding to fp16 (the reference's write_result, fp6_marlin_cuda_kernel.cu:698-749,
+ * only scales and stores; its layer lists name the neighbours, bench.py:53-86):
+ *   FP6M_EPILOGUE_SILU_MUL  gate / up projection in one matrix whose columns 2j and 2j+1 - inside the INT4
+ *                           region and inside the FP6 region - are gate_j and up_j: C is M x N/2 and receives
+ *                           silu(gate_j) * up_j, INT4 pairs first, then FP6 pairs;
+ *   FP6M_EPILOGUE_RESIDUAL  C = A W + residual, residual an M x N fp16 matrix laid out like C (may be C).
+ * FP6M_EPILOGUE_NONE makes it fp6m_mul.  Everything else as fp6m_mul.  No counterpart in the reference. */
+enum { FP6M_EPILOGUE_NONE = 0, FP6M_EPILOGUE_SILU_MUL = 1, FP6M_EPILOGUE_RESIDUAL = 2 };
+int fp6m_mul_fused(const void* A, const void* B, void* C, const void* s, int M, int N, int K,
+                   void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
+                   int dev, void* stream, int thread_k, int thread_n, int sms, int max_par,
+                   int quant_cols, int group_size, int layout, int* status_dev, int epilogue, const void* residual);
+
 /* Same GEMM as fp6m_mul for callers that may not allocate device memory at all: plug-ins living
  * inside a host runtime that owns the whole memory arena, code running after an allocator freeze
  * or while other threads hold the device in a state where cudaMalloc's implicit synchronisation is
@@ -191,6 +205,15 @@ int fp6m_pack_b200_device(const void* q4, const void* c6, const void* s4, const 
  * kernel that precedes a GEMM in its stream does not write that GEMM's B or s.  No counterpart in the
  * reference. */
 int fp6m_set_launch_overlap(int enable);
+
+/* Process-wide option, off by default; returns the previous setting (a negative argument only queries).
+ * The GEMM for up to 16 rows of A normally lets two threads issue the tensor-core instructions of one
+ * 128-row block, one per 64-row half, into one accumulator: the hardware may retire the halves in either
+ * order, so the last bit of a result can differ between two runs on the same inputs (same products, same
+ * fp32 adds, different order).  When on, one thread issues a block's instructions in a fixed order and two
+ * runs agree bit for bit, at some cost in speed.  The reference's serial, lock-ordered reduction is
+ * deterministic (fp6_marlin_cuda_kernel.cu:645-696). */
+int fp6m_set_ordered_sums(int enable);
 
 /* Message of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char* fp6m_last_cuda_error(void);

@@ -25,6 +25,7 @@ def test_wait_that_runs_out_sets_the_status_word_and_returns():
     a = synth.make_activations(m, k, 8).to(dev)
     workspace = torch.zeros(n // 128 * 16, dtype=torch.int32, device=dev)
     before = torch.zeros((m, n), dtype=torch.float16, device=dev)
+    ordered = fm.set_ordered_sums(True)          # fixed order of additions: the two GEMMs below can be compared bit for bit
     fm.mul(a, w.B, before, w.s, workspace, qc, group_size=gs, layout="b200")
     torch.cuda.synchronize()
     assert fm.device_status(dev) == 0
@@ -58,5 +59,6 @@ def test_wait_that_runs_out_sets_the_status_word_and_returns():
     after = torch.zeros((m, n), dtype=torch.float16, device=dev)
     fm.mul(a, w.B, after, w.s, workspace, qc, group_size=gs, layout="b200")
     torch.cuda.synchronize()
+    fm.set_ordered_sums(ordered)
     assert torch.equal(before, after)
     assert fm.device_status(dev) == 0

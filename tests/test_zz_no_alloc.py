@@ -34,19 +34,30 @@ def test_static_scratch_entry_point_matches_mul_twice():
     a = synth.make_activations(m, k, 5).to(dev)
     workspace = torch.zeros(n // 128 * 16, dtype=torch.int32, device=dev)
     expected = torch.zeros((m, n), dtype=torch.float16, device=dev)
-    fm.mul(a, w.B, expected, w.s, workspace, qc, group_size=gs, layout="b200")
-    torch.cuda.synchronize()
-    assert float(expected.float().abs().sum()) > 0
-    for attempt in range(2):
-        got = torch.full((m, n), float("nan"), dtype=torch.float16, device=dev)
-        rc = _call_static(a, w, got, workspace, qc, gs)
+    # with ordered sums the kernel adds in one fixed order, so that the two entry points can be compared bit for bit
+    previous = fm.set_ordered_sums(True)
+    try:
+        fm.mul(a, w.B, expected, w.s, workspace, qc, group_size=gs, layout="b200")
         torch.cuda.synchronize()
-        assert rc == _lib.OK, (attempt, rc, _lib.last_cuda_error())
-        # same kernel, same schedule, fixed summation order: the two entry points agree bit for bit,
-        # which is well inside the 1e-3 relative tolerance the other GPU tests use
-        err = (torch.linalg.norm(got.float() - expected.float()) / torch.linalg.norm(expected.float())).item()
-        assert err <= 1e-3, (attempt, err)
-        assert torch.equal(got, expected), attempt
+        assert float(expected.float().abs().sum()) > 0
+        for attempt in range(2):
+            got = torch.full((m, n), float("nan"), dtype=torch.float16, device=dev)
+            rc = _call_static(a, w, got, workspace, qc, gs)
+            torch.cuda.synchronize()
+            assert rc == _lib.OK, (attempt, rc, _lib.last_cuda_error())
+            # same kernel, same schedule, fixed summation order: the two entry points agree bit for bit,
+            # which is well inside the 1e-3 relative tolerance the other GPU tests use
+            err = (torch.linalg.norm(got.float() - expected.float()) / torch.linalg.norm(expected.float())).item()
+            assert err <= 1e-3, (attempt, err)
+            assert torch.equal(got, expected), attempt
+    finally:
+        fm.set_ordered_sums(previous)
+    # and in the default mode, where the halves of a block may be added in either order, within the tolerance
+    got = torch.full((m, n), float("nan"), dtype=torch.float16, device=dev)
+    assert _call_static(a, w, got, workspace, qc, gs) == _lib.OK
+    torch.cuda.synchronize()
+    err = (torch.linalg.norm(got.float() - expected.float()) / torch.linalg.norm(expected.float())).item()
+    assert err <= 1e-3, err
     assert int(workspace.abs().sum()) == 0
     assert fm.device_status(dev) == 0
 
