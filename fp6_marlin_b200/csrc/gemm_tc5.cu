@@ -87,7 +87,7 @@ struct Tc5Cfg {
   static constexpr int kEpiBase = kDeqBase + 4 * kTeams;
   static constexpr int kEpiSets = 2;
   static constexpr int kThreads = 32 * (kEpiBase + 4 * kEpiSets);
-  static_assert(STAGES_ <= 4 * kTeams + 4 * kEpiSets, "the first round of weight copies is issued by one warp per stage");
+  static_assert(kTeams >= 2 && STAGES_ <= 4 * kTeams + 4 * kEpiSets, "the first round of weight copies is issued by one warp per stage");
   static constexpr int kEpochWarp = 2 + kIssuers - 1;
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kStages = STAGES_;              // shared-memory stages of packed words (one segment each)
@@ -293,6 +293,111 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     }
   };
 
+  // ---- pieces shared by the epilogue sets and the dequantiser teams (thread = weight column c of a strip)
+  const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
+  const int c = quarter * 32 + lane;               // weight column inside the strip = TMEM lane
+  struct Slice {
+    int strip_lin, strip, b0, b1;       // blocks [b0, b1) of the strip belong to this CTA
+    bool is6, group;
+  };
+  auto open_slice = [&](int strip_lin, int b0, int b1) {
+    Slice sl;
+    sl.strip_lin = strip_lin;
+    sl.is6 = strip_lin >= geo.strips4;
+    sl.strip = sl.is6 ? strip_lin - geo.strips4 : strip_lin;
+    sl.group = !sl.is6 && geo.groups > 1;
+    sl.b0 = b0;
+    sl.b1 = b1;
+    return sl;
+  };
+  auto column_scale = [&](const Slice& sl, bool writes) {
+    float col_scale = 1.f;      // per-channel INT4: s; FP6: s * 4096; group INT4: already applied
+    if (writes && !sl.group) {
+      const half* sp = p.S + (sl.is6 ? fp6_scale_offset(geo, sl.strip) : int4_scale_offset(geo, sl.strip, 0));
+      col_scale = __half2float(__ldg(sp + c)) * (sl.is6 ? 4096.f : 1.f);
+    }
+    return col_scale;
+  };
+  // Split-K without atomics or fences: a partial is stored as 64-bit words {fp32 value, tag}, the
+  // tag being the launch epoch + 1 (the epoch word lives in the scratch header and is advanced once
+  // per launch, see read_epoch_and_count, so every launch - also a replay of a captured graph - uses
+  // fresh tags and stale slots of earlier launches never match).
+  // The reducer of a strip is its LAST contributor in CTA order, i.e. the CTA whose slice reaches
+  // the end of the strip; that slice is the first one of the CTA, and the reduction is postponed to
+  // the CTA's end, when the other contributors have normally finished.  It then reads the slots of
+  // the lower-numbered contributors, spinning (bounded) on words whose tag has not arrived, sums in
+  // CTA order (deterministic) and writes C.  Only lower-numbered CTAs are waited for, and those were
+  // dispatched earlier.  Only the first and the last slice of a CTA can be partial; the caller's
+  // workspace is not touched.
+  auto slot_of = [&](int cc, int strip_lin) {
+    // slot 0 holds the partial of a CTA's first strip, slot 1 that of its last strip
+    const int cc_first = (p.sched.bound[cc] >> 1) / kb;
+    return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
+  };
+  // After its last segment: the strip whose LAST contributor (in CTA order) this CTA is - the strip its range
+  // starts inside of and runs to the end of.  Four groups of 128 threads take part, each with a quarter of the
+  // rows: the two epilogue sets and the first two dequantiser teams (which have nothing else left to do), so
+  // that the tagged words of up to four contributors travel together, sixteen loads in flight per thread.  A
+  // value is added in CTA order, so the sum does not depend on the timing.
+  auto reduce_shared_strip = [&](int group) {
+    if (!(blk_first > 0 && nseg >= kb - blk_first)) return;         // this CTA is no strip's last contributor
+    constexpr int RR = NT / 4;                                       // rows of this thread
+    constexpr int kChunk = RR < 16 ? RR : 16;                        // rows per round
+    constexpr int kBatch = 16 / kChunk;                              // contributors per round
+    const int rr0 = group * RR;
+    const int reduce_strip = s_first;
+    mbar_wait(epoch_bar, 0, ws);                                     // completed long ago: orders the read of misc[1]
+    const uint32_t reduce_tag = misc[1] + 1;
+    const Slice sl = open_slice(reduce_strip, 0, kb);
+    const int s_begin = reduce_strip * kb;         // first block of the strip
+    int c_lo = cta;
+    while (c_lo > 0 && (p.sched.bound[c_lo] >> 1) > s_begin) --c_lo;
+    float sum[RR];
+#pragma unroll
+    for (int m = 0; m < RR; ++m) sum[m] = 0.f;
+#pragma unroll 1
+    for (int cbase = c_lo; cbase <= cta; cbase += kBatch) {
+      bool live[kBatch];
+      const unsigned long long* src[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const int cc = cbase + i;
+        live[i] = cc <= cta && p.sched.bound[cc] < p.sched.bound[cc + 1];       // a CTA without work stored nothing
+        src[i] = slot_of(live[i] ? cc : cta, reduce_strip) + rr0 * kStripCols;
+      }
+#pragma unroll
+      for (int m0 = 0; m0 < RR; m0 += kChunk) {
+        unsigned long long v[kBatch][kChunk];
+        bool all_here = false;
+#pragma unroll 1
+        for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+            for (int m = 0; m < kChunk; ++m) v[i][m] = ld_relaxed_u64(src[i] + (m0 + m) * kStripCols);
+          all_here = true;
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+            for (int m = 0; m < kChunk; ++m) all_here = all_here && (!live[i] || (uint32_t)(v[i][m] >> 32) == reduce_tag);
+          if (ws.failed) break;                       // a wait of this thread ran out before: do not wait again
+          if (!all_here) __nanosleep(64);             // the teams arrive here early: leave the issue slots to the others
+        }
+        if (!all_here) ws.failed = 1;
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+          for (int m = 0; m < kChunk; ++m) sum[m0 + m] += live[i] ? __uint_as_float((uint32_t)v[i][m]) : 0.f;
+      }
+    }
+    const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+    const bool writes = c < ncols;
+    const float col_scale = column_scale(sl, writes);
+#pragma unroll
+    for (int m = 0; m < RR; ++m) sum[m] *= col_scale;
+    store_column_rows<RR>(p, rr0, sl.is6, sl.strip * kStripCols + c, sum, writes);
+  };
+
   if (warp == 0) {
     // ================================================================== weights producer, segments S..
     if (lane == 0 && nseg > S) {
@@ -397,8 +502,6 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     // ================================================================== dequantisers
     // thread = weight column = TMEM lane; team t expands the segments n = t, t + T, ...
     const int team = (warp - C::kDeqBase) >> 2;
-    const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
-    const int c = quarter * 32 + lane;               // weight column inside the strip = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t a_base = lane_base + C::kTmemA;       // + r * 64
     const uint32_t d_base = lane_base + C::kTmemD;       // + r * NT
@@ -491,6 +594,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       if (r >= R) { r -= R; rphase ^= 1; }
       n = n_next;
     }
+    if (team < 2) reduce_shared_strip(2 + team);     // groups 0 and 1 are the epilogue sets
   } else if (warp >= C::kEpiBase) {
     // ================================================================== epilogue
     // Two sets of one warp per lane quarter; thread = weight column.  Set e reads the accumulator tiles of
@@ -498,52 +602,10 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     // sums to set 0, which writes the slice out (sums added in the order set 0 + set 1: fixed).
     constexpr int kEpiThreads = 128 * C::kEpiSets;
     const int eset = (warp - C::kEpiBase) >> 2;
-    const int quarter = warp & 3;
-    const int c = quarter * 32 + lane;
     const uint32_t d_base = tmem + ((uint32_t)(quarter * 32) << 16) + C::kTmemD;       // + r * NT
 
-    struct Slice {
-      int strip_lin, strip, b0, b1;       // blocks [b0, b1) of the strip belong to this CTA
-      bool is6, group;
-    };
-    auto open_slice = [&](int strip_lin, int b0, int b1) {
-      Slice sl;
-      sl.strip_lin = strip_lin;
-      sl.is6 = strip_lin >= geo.strips4;
-      sl.strip = sl.is6 ? strip_lin - geo.strips4 : strip_lin;
-      sl.group = !sl.is6 && geo.groups > 1;
-      sl.b0 = b0;
-      sl.b1 = b1;
-      return sl;
-    };
-    auto column_scale = [&](const Slice& sl, bool writes) {
-      float col_scale = 1.f;      // per-channel INT4: s; FP6: s * 4096; group INT4: already applied
-      if (writes && !sl.group) {
-        const half* sp = p.S + (sl.is6 ? fp6_scale_offset(geo, sl.strip) : int4_scale_offset(geo, sl.strip, 0));
-        col_scale = __half2float(__ldg(sp + c)) * (sl.is6 ? 4096.f : 1.f);
-      }
-      return col_scale;
-    };
-    // Split-K without atomics or fences: a partial is stored as 64-bit words {fp32 value, tag}, the
-    // tag being the launch epoch + 1 (the epoch word lives in the scratch header and is advanced once
-    // per launch, see read_epoch_and_count, so every launch - also a replay of a captured graph - uses
-    // fresh tags and stale slots of earlier launches never match).
-    // The reducer of a strip is its LAST contributor in CTA order, i.e. the CTA whose slice reaches
-    // the end of the strip; that slice is the first one of the CTA, and the reduction is postponed to
-    // the CTA's end, when the other contributors have normally finished.  It then reads the slots of
-    // the lower-numbered contributors, spinning (bounded) on words whose tag has not arrived, sums in
-    // CTA order (deterministic) and writes C.  Only lower-numbered CTAs are waited for, and those were
-    // dispatched earlier.  Only the first and the last slice of a CTA can be partial; the caller's
-    // workspace is not touched.
-    auto slot_of = [&](int cc, int strip_lin) {
-      // slot 0 holds the partial of a CTA's first strip, slot 1 that of its last strip
-      const int cc_first = (p.sched.bound[cc] >> 1) / kb;
-      return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
-    };
     constexpr int ROWS = C::kEpiRows;
     const int row0 = C::kRowSplit ? eset * ROWS : 0;          // this set's rows of A and C (all of them when the sets take turns)
-    int reduce_strip = -1;                           // strip this CTA must reduce at its end
-    uint32_t reduce_tag = 0;
     auto write_strip = [&](const Slice& sl, const float (&v)[ROWS]) {
       const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
       const bool writes = c < ncols;
@@ -564,69 +626,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #pragma unroll
       for (int m = 0; m < ROWS; ++m)
         st_relaxed_u64(slot + m * kStripCols, ((unsigned long long)tag << 32) | __float_as_uint(out[m]));
-      if (sl.b1 == kb) {                             // last contributor of the strip: reduce it at the end
-        reduce_strip = sl.strip_lin;
-        reduce_tag = tag;
-      }
     };
-    // After the last slice: the strip whose last contributor this CTA is.  Both epilogue sets take part, each
-    // with its share of the rows; sixteen tagged words travel together per thread (two contributors at a time
-    // for eight rows), and a value is added in CTA order, so the sum does not depend on the timing.
-    auto finish_cta = [&]() {
-      if (reduce_strip < 0) return;
-      constexpr int RR = C::kRowSplit ? ROWS : NT / C::kEpiSets;      // rows this thread reduces
-      const int rr0 = C::kRowSplit ? row0 : eset * RR;
-      constexpr int kChunk = RR < 16 ? RR : 16;                       // rows per round
-      constexpr int kBatch = 16 / kChunk;                             // contributors per round: 16 tagged words in flight per thread
-      const Slice sl = open_slice(reduce_strip, 0, kb);
-      const int s_begin = reduce_strip * kb;         // first block of the strip
-      int c_lo = cta;
-      while (c_lo > 0 && (p.sched.bound[c_lo] >> 1) > s_begin) --c_lo;
-      float sum[RR];
-#pragma unroll
-      for (int m = 0; m < RR; ++m) sum[m] = 0.f;
-#pragma unroll 1
-      for (int cbase = c_lo; cbase <= cta; cbase += kBatch) {
-        bool live[kBatch];
-        const unsigned long long* src[kBatch];
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i) {
-          const int cc = cbase + i;
-          live[i] = cc <= cta && p.sched.bound[cc] < p.sched.bound[cc + 1];       // a CTA without work stored nothing
-          src[i] = slot_of(live[i] ? cc : cta, reduce_strip) + rr0 * kStripCols;
-        }
-#pragma unroll
-        for (int m0 = 0; m0 < RR; m0 += kChunk) {
-          unsigned long long v[kBatch][kChunk];
-          bool all_here = false;
-#pragma unroll 1
-          for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i)
-#pragma unroll
-              for (int m = 0; m < kChunk; ++m) v[i][m] = ld_relaxed_u64(src[i] + (m0 + m) * kStripCols);
-            all_here = true;
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i)
-#pragma unroll
-              for (int m = 0; m < kChunk; ++m) all_here = all_here && (!live[i] || (uint32_t)(v[i][m] >> 32) == reduce_tag);
-            if (ws.failed) break;                       // a wait of this thread ran out before: do not wait again
-          }
-          if (!all_here) ws.failed = 1;
-#pragma unroll
-          for (int i = 0; i < kBatch; ++i)
-#pragma unroll
-            for (int m = 0; m < kChunk; ++m) sum[m0 + m] += live[i] ? __uint_as_float((uint32_t)v[i][m]) : 0.f;
-        }
-      }
-      const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
-      const bool writes = c < ncols;
-      const float col_scale = column_scale(sl, writes);
-#pragma unroll
-      for (int m = 0; m < RR; ++m) sum[m] *= col_scale;
-      store_column_rows<RR>(p, rr0, sl.is6, sl.strip * kStripCols + c, sum, writes);
-    };
-
     float acc[ROWS];
 #pragma unroll
     for (int m = 0; m < ROWS; ++m) acc[m] = 0.f;
@@ -669,11 +669,6 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #pragma unroll
         for (int m = 0; m < ROWS; ++m) sts_f32(xch + (m * kStripCols + c) * 4, acc[m]);
         named_bar_arrive(1, kEpiThreads);
-        if (!(sl.b0 == 0 && sl.b1 == kb) && sl.b1 == kb) {      // as set 0 finds in finish_slice: this CTA reduces the strip
-          mbar_wait(epoch_bar, 0, ws);
-          reduce_strip = sl.strip_lin;
-          reduce_tag = misc[1] + 1;
-        }
       } else {
         named_bar_sync(1, kEpiThreads);
 #pragma unroll
@@ -685,7 +680,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #pragma unroll
       for (int m = 0; m < ROWS; ++m) acc[m] = 0.f;
     }
-    finish_cta();
+    reduce_shared_strip(eset);
     FP6M_TRACE_EVENT(trace, 23, 0);
   }
 
