@@ -250,8 +250,20 @@ _sm_count: dict[int, int] = {}
 _prepared: dict[int, tuple] = {}
 
 
-def _device_buffers(device: torch.device, shape=None):
-    """(device index, split-K scratch, status word) for a GEMM on the CURRENT stream of `device`.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_scratch_need: dict[tuple, int] = {}
+
+
+def _stream_handle(idx: int, device: torch.device) -> int:
+    """The cudaStream_t of the current torch stream of `device`."""
+    if _raw_stream is not None:
+        return _raw_stream(idx)
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _device_buffers(device: torch.device, shape=None, stream=None):
+    """(device index, split-K scratch, status word) for a GEMM on the CURRENT stream of `device`
+    (`stream`: its handle, if the caller has it already).
 
     The scratch holds the launch epoch and the tagged split-K slots of the kernels, so two GEMMs that
     can overlap on the GPU must not share one: there is one buffer per (device, stream), created (and
@@ -263,11 +275,17 @@ def _device_buffers(device: torch.device, shape=None):
     if idx not in _status:
         _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
         _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    if shape is None:
-        nbytes = lib.fp6m_mul_scratch_bytes(16, 1 << 20, 1 << 14, 0, _sm_count[idx])
-    else:
-        nbytes = lib.fp6m_mul_scratch_bytes(shape[0], shape[1], shape[2], shape[3], _sm_count[idx])
-    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    need_key = (idx, shape)
+    nbytes = _scratch_need.get(need_key)
+    if nbytes is None:
+        if shape is None:
+            nbytes = lib.fp6m_mul_scratch_bytes(16, 1 << 20, 1 << 14, 0, _sm_count[idx])
+        else:
+            nbytes = lib.fp6m_mul_scratch_bytes(shape[0], shape[1], shape[2], shape[3], _sm_count[idx])
+        if len(_scratch_need) > 4096:
+            _scratch_need.clear()
+        _scratch_need[need_key] = nbytes
+    key = (idx, _stream_handle(idx, device) if stream is None else stream)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         # zero once: the kernels keep the epoch and the tagged slots in it between calls
@@ -365,8 +383,9 @@ def mul(A, B, C, s, workspace, quant_cols=-1, thread_k=-1, thread_n=-1, sms=-1, 
     elif layout != "b200":
         raise RuntimeError(f"mul: unknown layout {layout!r}")
 
-    dev_index, scratch, status = _device_buffers(A.device, (M, N, K, quant_cols))
-    stream = torch.cuda.current_stream(A.device).cuda_stream
+    device = A.device
+    stream = _stream_handle(device.index if device.index is not None else torch.cuda.current_device(), device)
+    dev_index, scratch, status = _device_buffers(device, (M, N, K, quant_cols), stream)
     rc = lib.fp6m_mul(_ptr(A), _ptr(B), _ptr(C), _ptr(s), M, N, K,
                       _ptr(workspace), workspace.numel() * workspace.element_size(),
                       _ptr(scratch), scratch.numel(), dev_index, stream,
@@ -420,8 +439,9 @@ def mul_fused(A, B, C, s, workspace, quant_cols=-1, *, epilogue="none", residual
         res_ptr = _ptr(residual)
     if M == 0 or N == 0 or K == 0:
         return
-    dev_index, scratch, status = _device_buffers(A.device, (M, N, K, quant_cols))
-    stream = torch.cuda.current_stream(A.device).cuda_stream
+    device = A.device
+    stream = _stream_handle(device.index if device.index is not None else torch.cuda.current_device(), device)
+    dev_index, scratch, status = _device_buffers(device, (M, N, K, quant_cols), stream)
     rc = lib.fp6m_mul_fused(_ptr(A), _ptr(B), _ptr(C), _ptr(s), M, N, K,
                             _ptr(workspace), workspace.numel() * workspace.element_size(),
                             _ptr(scratch), scratch.numel(), dev_index, stream,

@@ -58,10 +58,6 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity,
   constexpr uint32_t kSleep = kSleepNs > 0 ? kSleepNs : 1;
   constexpr uint32_t kLimit = 1u << 24;                       // x (sleep + poll) of at least ~60 ns each: about a second
   uint32_t ok;
-#ifndef FP6M_WAIT_MODE
-#define FP6M_WAIT_MODE 0
-#endif
-#if FP6M_WAIT_MODE == 0
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
@@ -81,48 +77,6 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity,
       : "=r"(ok)
       : "r"(bar), "r"(parity), "n"(kSleep), "n"(kLimit)
       : "memory");
-#elif FP6M_WAIT_MODE == 1
-  // no sleep; try_wait with a long suspend-time hint
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .u32 i;\n"
-      "mov.u32 i, 0;\n"
-      "FP6M_WAIT_LOOP:\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "@p bra FP6M_WAIT_DONE;\n"
-      "add.u32 i, i, 1;\n"
-      "setp.lt.u32 p, i, %4;\n"
-      "@p bra FP6M_WAIT_LOOP;\n"
-      "setp.ne.u32 p, 0, 0;\n"
-      "FP6M_WAIT_DONE:\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000000u), "n"(kLimit)
-      : "memory");
-#else
-  // long sleeps (4 x the grain) between polls
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .u32 i;\n"
-      "mov.u32 i, 0;\n"
-      "FP6M_WAIT_LOOP:\n"
-      "nanosleep.u32 %3;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "@p bra FP6M_WAIT_DONE;\n"
-      "add.u32 i, i, 1;\n"
-      "setp.lt.u32 p, i, %4;\n"
-      "@p bra FP6M_WAIT_LOOP;\n"
-      "setp.ne.u32 p, 0, 0;\n"
-      "FP6M_WAIT_DONE:\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "n"(kSleep * 6), "n"(kLimit)
-      : "memory");
-#endif
   if (ok) return;
   dead = true;
   if (status) atomicExch(status, kStatusTimeout);

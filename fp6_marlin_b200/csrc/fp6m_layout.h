@@ -184,12 +184,28 @@ FP6M_HD long long range_cost(const Geometry& g, int u0, int u1) {
 inline void make_schedule(const Geometry& g, int ctas, Schedule* out, int row_tiles = 1) {
   if (ctas > kMaxCtas) ctas = kMaxCtas;
   if (ctas < 1) ctas = 1;
-  const int total_units = row_tiles * (g.strips4 + g.strips6) * units_per_strip(g);
-  const long long total_cost = range_cost(g, 0, total_units);
+  const int ups = units_per_strip(g);
+  const int nstrips = g.strips4 + g.strips6;
+  const int total_units = row_tiles * nstrips * ups;
+  const long long total_cost = (long long)row_tiles * ups * (8ll * g.strips4 + 9ll * g.strips6);
   out->ctas = ctas;
   out->total_units = total_units;
-  for (int c = 0; c <= ctas; ++c)
-    out->bound[c] = c == ctas ? total_units : unit_at_cost(g, 0, total_units, total_cost * c / ctas);
+  // bound[c] = unit_at_cost(g, 0, total_units, total_cost * c / ctas), all of them in one walk over the
+  // strips (the targets rise with c)
+  int strip = 0, real = 0;          // the strip the walk is in; its index among the strips of one row tile
+  long long acc = 0;                // cost of the units before that strip
+  for (int c = 0; c < ctas; ++c) {
+    const long long target = total_cost * c / ctas;
+    int cost = real < g.strips4 ? 8 : 9;
+    while (acc + (long long)ups * cost <= target) {
+      acc += (long long)ups * cost;
+      ++strip;
+      if (++real == nstrips) real = 0;
+      cost = real < g.strips4 ? 8 : 9;
+    }
+    out->bound[c] = strip * ups + (int)((target - acc + cost - 1) / cost);
+  }
+  out->bound[ctas] = total_units;
 }
 
 // Moves every inner boundary to a whole block (an even unit): the kernel for up to 16 rows works on

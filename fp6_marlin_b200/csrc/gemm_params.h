@@ -55,7 +55,10 @@ constexpr int kEpochWords = 64;     // scratch header size in 32-bit words
 // gemm_tc5.cu
 int tc5_ctas_per_sm(int rows);
 int tc5_tile_rows(int rows);
-constexpr int kTc5MaxRows = 64;     // rows of A the kernel of gemm_tc5.cu covers; more rows go to gemm_wide.cu
+#ifndef FP6M_TC5_MAX_ROWS
+#define FP6M_TC5_MAX_ROWS 128
+#endif
+constexpr int kTc5MaxRows = FP6M_TC5_MAX_ROWS;     // rows of A the kernel of gemm_tc5.cu covers; more rows go to gemm_wide.cu
 size_t tc5_scratch_bytes(int ctas, int rows);
 void tc5_set_overlap(bool on);
 bool tc5_get_overlap();

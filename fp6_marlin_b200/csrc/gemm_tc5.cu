@@ -71,7 +71,7 @@ namespace fp6m {
 
 namespace {
 
-template <int NT_, int STAGES_, int RING_, int TEAMS_, bool SPLIT_ISSUE_>
+template <int NT_, int STAGES_, int RING_, int TEAMS_, bool SPLIT_ISSUE_, int DRING_ = RING_>
 struct Tc5Cfg {
   static constexpr int kTeams = TEAMS_;
   // Two issuers per team.  kSplitIssue: both work on every segment of the team, one 64-row unit each, adding to
@@ -85,13 +85,20 @@ struct Tc5Cfg {
   // the four epilogue warps
   static constexpr int kDeqBase = (2 + kIssuers + 3) & ~3;
   static constexpr int kEpiBase = kDeqBase + 4 * kTeams;
-  static constexpr int kEpiSets = 2;
+  static constexpr int kEpiSets = NT_ > 64 ? 4 : 2;       // a thread of an epilogue set accumulates at most 32 rows
   static constexpr int kThreads = 32 * (kEpiBase + 4 * kEpiSets);
   static_assert(kTeams >= 2 && STAGES_ <= 4 * kTeams + 4 * kEpiSets, "the first round of weight copies is issued by one warp per stage");
   static constexpr int kEpochWarp = 2 + kIssuers - 1;
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kStages = STAGES_;              // shared-memory stages of packed words (one segment each)
-  static constexpr int kRing = RING_;                  // ring of {activation tile, TMEM operand slot, accumulator tile}
+  static constexpr int kRing = RING_;                  // ring of {activation tile, TMEM operand slot}
+  // Accumulator tiles.  kDRing == kRing: every ring entry has its own tile, the team that fills the entry
+  // zeroes it.  Fewer tiles (wide tiles do not fit six times): segment n uses tile n % kDRing, the epilogue
+  // zeroes a tile after reading it and hands it to the issuers of segment n + kDRing.
+  static constexpr int kDRing = DRING_;
+  static constexpr bool kDecoupled = kDRing != kRing;
+  static_assert(kDRing <= kRing && kDRing % 2 == 0, "accumulator tiles");
+  static_assert(!kDecoupled || NT_ > 16, "with fewer tiles than entries both epilogue sets read every segment");
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves
   static constexpr int kActBytes = 2 * kActUnitBytes;
   static constexpr int kNumBars = 2 * kStages + 4 * kRing + 1;
@@ -101,15 +108,17 @@ struct Tc5Cfg {
 
   static_assert(kRing <= kIssuers, "the first round of activation copies is issued by one issuer warp per entry");
   static_assert(kRing == 2 * kTeams, "each team owns two ring entries (one per issuer when the issuers take turns)");
-  static constexpr int kScaleRingBytes = kRing * kStripCols * 4;   // the group scale (fp16 bits in a word) of every column of the segment in a ring entry
+  // the group scale (fp16 bits in a word) of every column of the segment in a ring entry; with fewer
+  // accumulator tiles than entries a team may be a whole round ahead of the epilogue: two sets of scales
+  static constexpr int kScaleRingBytes = (kDecoupled ? 2 : 1) * kRing * kStripCols * 4;
   // Up to 16 rows the two epilogue sets take the segments in turn and pool their sums at the end of a slice;
   // with more rows each set reads its half of the rows of every segment (the sums would not fit in registers).
   static constexpr bool kRowSplit = NT > 16;
   static constexpr int kEpiRows = kRowSplit ? NT / kEpiSets : NT;     // rows a thread of an epilogue set accumulates
   static constexpr int kXchBytes = kRowSplit ? 0 : NT * kStripCols * 4;   // the second epilogue set's sums of a slice
-  static_assert(kRing % kEpiSets == 0, "a ring entry always belongs to the same epilogue set");
+  static_assert(kRowSplit || kRing % kEpiSets == 0, "a ring entry always belongs to the same epilogue set");
   static constexpr int kSmemBytes = kStages * kStageW + kRing * kActBytes + kScaleRingBytes + kXchBytes + kNumBars * 8 + 64 + 1024;   // + alignment slack
-  static constexpr int kTmemD = 0, kTmemA = kRing * NT;  // accumulator tiles, then operand slots of 64 columns
+  static constexpr int kTmemD = 0, kTmemA = kDRing * NT;  // accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
   static_assert(kTmemUsed <= 512, "tensor memory has 512 columns");
@@ -218,6 +227,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   const unsigned long long t_launch = global_ns();
 #endif
   launch_dependents();
+  if (tid == 32) prefetch_tensormap(&amap);        // the first activation copy then finds the descriptor cached
   if (nseg <= 0) {                     // no work: still counted, see read_epoch_and_count
     if (tid == 0) {
       grid_dependency_wait();
@@ -270,6 +280,8 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   const uint32_t tmem = misc[0];
   // Everything below depends, directly or through the MMAs, on the activations, which the previous
   // kernel of the stream may still be writing: all bounded waits start after it has completed.
+  // (Letting the dequantiser teams expand their first segments before this wait was measured: no gain
+  // on a chain of GEMMs - a step is as long as the life of the CTAs that start last.)
   grid_dependency_wait();
   FP6M_TRACE_EVENT(trace, 4, 0);
 
@@ -336,14 +348,17 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   };
   // After its last segment: the strip whose LAST contributor (in CTA order) this CTA is - the strip its range
   // starts inside of and runs to the end of.  Four groups of 128 threads take part, each with a quarter of the
-  // rows: the two epilogue sets and the first two dequantiser teams (which have nothing else left to do), so
-  // that the tagged words of up to four contributors travel together, sixteen loads in flight per thread.  A
-  // value is added in CTA order, so the sum does not depend on the timing.
+  // rows: the epilogue sets and, where there are only two of those, the first two dequantiser teams (which
+  // have nothing else left to do), so that the tagged words of up to four contributors travel together.  A
+  // value is added in CTA order, so the sum does not depend on the timing.  (Measured and dropped: giving
+  // all of it to the warps that run out of work first - teams, issuers - ends the reducing CTAs earlier but
+  // lengthened the step of the square layer by 4 %.)
   auto reduce_shared_strip = [&](int group) {
     if (!(blk_first > 0 && nseg >= kb - blk_first)) return;         // this CTA is no strip's last contributor
     constexpr int RR = NT / 4;                                       // rows of this thread
-    constexpr int kChunk = RR < 16 ? RR : 16;                        // rows per round
-    constexpr int kBatch = 16 / kChunk;                              // contributors per round
+    constexpr int kInFlight = NT > 64 ? 8 : 16;                      // 64-bit loads in flight per thread (registers)
+    constexpr int kChunk = RR < kInFlight ? RR : kInFlight;          // rows per round
+    constexpr int kBatch = kInFlight / kChunk;                       // contributors per round
     const int rr0 = group * RR;
     const int reduce_strip = s_first;
     mbar_wait(epoch_bar, 0, ws);                                     // completed long ago: orders the read of misc[1]
@@ -355,6 +370,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     float sum[RR];
 #pragma unroll
     for (int m = 0; m < RR; ++m) sum[m] = 0.f;
+    FP6M_TRACE_EVENT(trace, 25, group);
 #pragma unroll 1
     for (int cbase = c_lo; cbase <= cta; cbase += kBatch) {
       bool live[kBatch];
@@ -384,6 +400,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
           if (!all_here) __nanosleep(64);             // the teams arrive here early: leave the issue slots to the others
         }
         if (!all_here) ws.failed = 1;
+        FP6M_TRACE_EVENT(trace, 26, group);
 #pragma unroll
         for (int i = 0; i < kBatch; ++i)
 #pragma unroll
@@ -396,6 +413,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #pragma unroll
     for (int m = 0; m < RR; ++m) sum[m] *= col_scale;
     store_column_rows<RR>(p, rr0, sl.is6, sl.strip * kStripCols + c, sum, writes);
+    FP6M_TRACE_EVENT(trace, 27, group);
   };
 
   if (warp == 0) {
@@ -461,9 +479,10 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       for (int n = team; n < nseg; n += T) {
         mbar_wait<32>(ready + 8 * r, rphase, ws);
         mbar_wait<32>(act_full + 8 * r, rphase, ws);
+        if constexpr (C::kDecoupled) mbar_wait<32>(d_free + 8 * r, rphase, ws);      // the entry's accumulator tile is free and zero
         tc_fence_after();
         FP6M_TRACE_EVENT(trace, 6, n);
-        const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
+        const uint32_t d_tmem = tmem + C::kTmemD + (C::kDecoupled ? n % C::kDRing : r) * NT;
         const uint32_t a_tmem = tmem + C::kTmemA + r * 64 + unit * 32;
         // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
         const uint64_t desc = desc0 + (uint64_t)(r * (C::kActBytes >> 4));
@@ -481,11 +500,12 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       const int r = mine;
       uint32_t rphase = 0;
       const uint64_t desc = wide_act_desc(act_base) + (uint64_t)(r * (C::kActBytes >> 4));
-      const uint32_t d_tmem = tmem + C::kTmemD + r * NT;
       const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
       for (int n = r; n < nseg; n += R) {
+        const uint32_t d_tmem = tmem + C::kTmemD + (C::kDecoupled ? n % C::kDRing : r) * NT;
         mbar_wait<32>(ready + 8 * r, rphase, ws);
         mbar_wait<32>(act_full + 8 * r, rphase, ws);
+        if constexpr (C::kDecoupled) mbar_wait<32>(d_free + 8 * r, rphase, ws);      // the entry's accumulator tile is free
         tc_fence_after();
         FP6M_TRACE_EVENT(trace, 6, n);
         if (lane == 0) {
@@ -556,14 +576,23 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #pragma unroll 1
     while (n < nseg) {
       FP6M_TRACE_EVENT(trace, 10, n);
-      // the epilogue has read the sums of the segment that used this ring entry before (so its MMAs are done too)
-      mbar_wait(d_free + 8 * r, rphase, ws);
+      if constexpr (C::kDecoupled) {
+        // the MMAs of the segment that used this ring entry before are done
+        mbar_wait(done + 8 * r, rphase, ws);
+      } else {
+        // the epilogue has read the sums of the segment that used this ring entry before (so its MMAs are done too)
+        mbar_wait(d_free + 8 * r, rphase, ws);
+      }
       tc_fence_after();
       FP6M_TRACE_EVENT(trace, 12, n);
       const uint32_t a_tmem = a_base + r * 64;
       // this column's scale of the block goes on to the epilogue warps
-      sts_u32(scale_ring + (r * kStripCols + c) * 4, w.scale_raw);
-      if constexpr (C::kSplitIssue) tc_st_zero<NT>(d_base + r * NT);       // both issuers' MMAs accumulate
+      if constexpr (C::kDecoupled) {
+        sts_u32(scale_ring + (((rphase ^ 1) * R + r) * kStripCols + c) * 4, w.scale_raw);     // rphase ^ 1: parity of this use
+      } else {
+        sts_u32(scale_ring + (r * kStripCols + c) * 4, w.scale_raw);
+        if constexpr (C::kSplitIssue) tc_st_zero<NT>(d_base + r * NT);       // both issuers' MMAs accumulate
+      }
       if (sp.is6) {
         expand_words<true>(w.lo0, w.hi0, w.two0, a_tmem);
         expand_words<true>(w.lo1, w.hi1, w.two1, a_tmem + 32);
@@ -594,7 +623,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       if (r >= R) { r -= R; rphase ^= 1; }
       n = n_next;
     }
-    if (team < 2) reduce_shared_strip(2 + team);     // groups 0 and 1 are the epilogue sets
+    if (C::kEpiSets == 2 && team < 2) reduce_shared_strip(2 + team);     // groups 0 and 1 are the epilogue sets (four sets need no help)
   } else if (warp >= C::kEpiBase) {
     // ================================================================== epilogue
     // Two sets of one warp per lane quarter; thread = weight column.  Set e reads the accumulator tiles of
@@ -634,27 +663,59 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     if (!C::kRowSplit && eset == 0) named_bar_arrive(2, kEpiThreads);       // the exchange buffer starts out free
     int n = C::kRowSplit ? 0 : eset, r = n, n_first = 0;    // n_first: first segment of the current slice
     uint32_t rphase = 0;
+    if constexpr (C::kDecoupled) {
+      // the accumulator tiles start out free; when two issuers add to a tile it must start out zero
+      if constexpr (C::kSplitIssue) {
+#pragma unroll
+        for (int d = 0; d < C::kDRing; ++d) tc_st_zero<ROWS>(d_base + d * NT + row0);
+        tc_wait_st();
+        tc_fence_before();
+      }
+#pragma unroll
+      for (int d = 0; d < C::kDRing; ++d) mbar_arrive(d_free + 8 * d);
+    }
     for (int s = s_first; n_first < nseg; ++s) {
       const int b0 = s == s_first ? blk_first : 0;
       const int n_end = min(nseg, (s + 1) * kb - B0);
       const Slice sl = open_slice(s, b0, b0 + (n_end - n_first));
 #pragma unroll 1
       for (; n < n_end; n += kStep) {
-        // the team's arrival on `ready` published the column scales of this entry
-        mbar_wait(ready + 8 * r, rphase, ws);
-        const float scale = __half2float(__ushort_as_half((unsigned short)lds_u32(scale_ring + (r * kStripCols + c) * 4)));
-        mbar_wait(done + 8 * r, rphase, ws);
+        float scale;
+        uint32_t d_tile;
+        if constexpr (C::kDecoupled) {
+          // (No wait on `ready`: the team may complete the entry's next phase of it before this thread gets here;
+          // `done` cannot run ahead, the next MMAs into this tile wait for this thread.)
+          mbar_wait(done + 8 * r, rphase, ws);
+          scale = __half2float(__ushort_as_half((unsigned short)lds_u32(scale_ring + ((rphase * R + r) * kStripCols + c) * 4)));
+          d_tile = d_base + (n % C::kDRing) * NT + row0;
+        } else {
+          // the team's arrival on `ready` published the column scales of this entry
+          mbar_wait(ready + 8 * r, rphase, ws);
+          scale = __half2float(__ushort_as_half((unsigned short)lds_u32(scale_ring + (r * kStripCols + c) * 4)));
+          mbar_wait(done + 8 * r, rphase, ws);
+          d_tile = d_base + r * NT + row0;
+        }
         tc_fence_after();
         FP6M_TRACE_EVENT(trace, 15, n);
 #pragma unroll
         for (int m0 = 0; m0 < ROWS; m0 += 16) {
           float d[16];
-          tc_ld16(d_base + r * NT + row0 + m0, d);
+          tc_ld16(d_tile + m0, d);
 #pragma unroll
           for (int i = 0; i < 16; ++i) acc[m0 + i] = fmaf(scale, d[i], acc[m0 + i]);
         }
-        tc_fence_before();
-        mbar_arrive(d_free + 8 * r);                    // the team may zero the tile for its next segment
+        if constexpr (C::kDecoupled) {
+          if constexpr (C::kSplitIssue) {
+            tc_st_zero<ROWS>(d_tile);
+            tc_wait_st();
+          }
+          tc_fence_before();
+          // the tile goes to the issuers of segment n + kDRing (ring entry (r + kDRing) % R)
+          mbar_arrive(d_free + 8 * ((r + C::kDRing) % R));
+        } else {
+          tc_fence_before();
+          mbar_arrive(d_free + 8 * r);                  // the team may zero the tile for its next segment
+        }
         FP6M_TRACE_EVENT(trace, 16, n);
         r += kStep;
         if (r >= R) { r -= R; rphase ^= 1; }
@@ -706,12 +767,27 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #endif
 using Tc5Rows16 = Tc5Cfg<16, FP6M_TC5_STAGES, 2 * FP6M_TC5_TEAMS, FP6M_TC5_TEAMS, true>;          // 3 teams: 6 x 16 + 6 x 64 = 480 TMEM columns
 using Tc5Rows16Ordered = Tc5Cfg<16, FP6M_TC5_STAGES, 2 * FP6M_TC5_TEAMS, FP6M_TC5_TEAMS, false>;  // one issuing thread per accumulator tile: run-to-run bit-identical
-// 17 to 64 rows: two teams, four ring entries (4 x 64 + 4 x 32 = 384, 4 x 64 + 4 x 64 = 512 TMEM columns); the
-// activation tiles grow with the rows, the weight stages give way
+// 17 to 64 rows: the tiles are too wide for six of them: two accumulator tiles (2 x 32 or 2 x 64 TMEM columns)
+// beside the six operand slots; the activation tiles grow with the rows, the weight stages give way
+#ifndef FP6M_TC5_WIDE_CFG
+#define FP6M_TC5_WIDE_CFG 1
+#endif
+#if FP6M_TC5_WIDE_CFG
+using Tc5Rows32 = Tc5Cfg<32, 12, 6, 3, true, 4>;
+using Tc5Rows32Ordered = Tc5Cfg<32, 12, 6, 3, false, 4>;
+using Tc5Rows64 = Tc5Cfg<64, 10, 4, 2, true>;
+using Tc5Rows64Ordered = Tc5Cfg<64, 10, 4, 2, false>;
+#else
 using Tc5Rows32 = Tc5Cfg<32, 14, 4, 2, true>;
 using Tc5Rows32Ordered = Tc5Cfg<32, 14, 4, 2, false>;
 using Tc5Rows64 = Tc5Cfg<64, 10, 4, 2, true>;
 using Tc5Rows64Ordered = Tc5Cfg<64, 10, 4, 2, false>;
+#endif
+
+// 65 to 128 rows: two teams, four operand slots (256 TMEM columns) beside two accumulator tiles of 128 columns;
+// four epilogue sets of 32 rows each
+using Tc5Rows128 = Tc5Cfg<128, 6, 4, 2, true, 2>;
+using Tc5Rows128Ordered = Tc5Cfg<128, 6, 4, 2, false, 2>;
 
 bool g_overlap_launches = false;
 bool g_ordered_sums = false;
@@ -765,19 +841,20 @@ bool tc5_get_overlap() { return g_overlap_launches; }
 // CTAs per SM the kernel is sized for, for `rows` rows of A in one pass.
 int tc5_ctas_per_sm(int rows) { (void)rows; return 1; }
 
-// rows of the MMA tile used for `rows` (<= 64) rows of A
-int tc5_tile_rows(int rows) { return rows <= 16 ? 16 : (rows <= 32 ? 32 : 64); }
+// rows of the MMA tile used for `rows` (<= kTc5MaxRows) rows of A
+int tc5_tile_rows(int rows) { return rows <= 16 ? 16 : (rows <= 32 ? 32 : (rows <= 64 ? 64 : 128)); }
 
 size_t tc5_scratch_bytes(int ctas, int rows) {
   return kEpochWords * sizeof(unsigned int) + (size_t)2 * ctas * tc5_tile_rows(rows) * kStripCols * sizeof(unsigned long long);
 }
 
-// Runs the GEMM for rows [0, p.M) with p.M <= 64.  The schedule's unit boundaries must be even (whole blocks).
+// Runs the GEMM for rows [0, p.M) with p.M <= kTc5MaxRows.  The schedule's unit boundaries must be even (whole blocks).
 cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream) {
   switch (tc5_tile_rows(p.M)) {
     case 16: return g_ordered_sums ? launch_tc5<Tc5Rows16Ordered>(p, stream) : launch_tc5<Tc5Rows16>(p, stream);
     case 32: return g_ordered_sums ? launch_tc5<Tc5Rows32Ordered>(p, stream) : launch_tc5<Tc5Rows32>(p, stream);
-    default: return g_ordered_sums ? launch_tc5<Tc5Rows64Ordered>(p, stream) : launch_tc5<Tc5Rows64>(p, stream);
+    case 64: return g_ordered_sums ? launch_tc5<Tc5Rows64Ordered>(p, stream) : launch_tc5<Tc5Rows64>(p, stream);
+    default: return g_ordered_sums ? launch_tc5<Tc5Rows128Ordered>(p, stream) : launch_tc5<Tc5Rows128>(p, stream);
   }
 }
 

@@ -85,6 +85,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   const int ups = units_per_strip(geo);
   const int U0 = p.sched.bound[cta], U1 = p.sched.bound[cta + 1];
   launch_dependents();
+  if (tid == 32) prefetch_tensormap(&amap);        // the first activation copy then finds the descriptor cached
   if (U0 >= U1) {                      // no work: still counted, see read_epoch_and_count
     if (tid == 0) {
       grid_dependency_wait();

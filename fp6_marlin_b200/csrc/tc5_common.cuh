@@ -2,6 +2,9 @@
 // tcgen05 / TMEM wrappers, gpu-scope relaxed accesses for the tagged split-K slots, the launch
 // epoch, the in-register expanders and the walk over a CTA's units.
 #pragma once
+#ifndef FP6M_PARTIAL_STORE_MODE
+#define FP6M_PARTIAL_STORE_MODE 0
+#endif
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -104,7 +107,13 @@ __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long
   return v;
 }
 __device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+#if FP6M_PARTIAL_STORE_MODE == 1
+  asm volatile("st.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+#elif FP6M_PARTIAL_STORE_MODE == 2
+  asm volatile("st.global.cg.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+#else
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+#endif
 }
 __device__ __forceinline__ uint32_t atomic_add_relaxed_u32(unsigned int* addr, uint32_t v) {
   uint32_t old;
@@ -167,6 +176,9 @@ __device__ __forceinline__ void store_column_rows(const Params& p, int row0, boo
 // the leading-dimension field is not used by swizzled K-major layouts
 __device__ __forceinline__ uint64_t wide_act_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 // k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
 __device__ __forceinline__ void tma_load_act(uint32_t dst, const CUtensorMap* map, int k0, uint32_t bar) {

@@ -58,7 +58,7 @@ def timeline(k, n, m):
     buf = np.zeros((CTAS_TRACED, WARPS, ENTRIES), dtype=np.uint64)
     rc = read(buf.ctypes.data, buf.nbytes)
     print("trace_read rc", rc, "device status", fm.device_status(dev))
-    teams = 3 if m <= 16 else 2
+    teams = 3 if m <= 64 else 2          # dequantiser teams of the kernel instance for m rows
     deq = (2 + 2 * teams + 3) & ~3
     epi = deq + 4 * teams
     for ci in range(CTAS_TRACED):
@@ -99,7 +99,12 @@ def timeline(k, n, m):
             s, r = seg[nn], got.get(nn, {})
             print(f"{nn:3d} | {s.get(10)!s:>6} {s.get(12)!s:>6} {s.get(17)!s:>6} {s.get(18)!s:>6} {s.get(19)!s:>6} {s.get(13)!s:>6} | "
                   f"{iss.get(nn, [])!s:>44} | {r.get(15)!s:>7} {r.get(16)!s:>7}")
-        print("end of the last slice / partial stored / strip reduced / CTA end:", [(t, tt) for (t, _, tt) in ev[epi] if t >= 20])
+        print("end of a slice (20) / its sums written or stored as a partial (22) / past the strip reduction (23) / CTA end (24):",
+              [(t, tt) for (t, _, tt) in ev[epi] if 20 <= t <= 24])
+        for w in list(range(deq, deq + 8, 4)) + list(range(epi, min(WARPS, epi + 16), 4)):
+            red = [(t, tt) for (t, _, tt) in ev[w] if t in (25, 26, 27)]
+            if red:
+                print(f"  strip reduction, warp {w}: entered (25) / a round's tagged words all present (26) / C written (27):", red)
 
 
 def launches(k, n, m):

@@ -9,6 +9,7 @@ The two extra ``-include`` flags supply headers the reference forgets (<cstdint>
 <cmath>) under g++ 13; nothing else about the sources is changed.
 
 Usage:  python oracle/build_ref.py [path-to-reference-checkout]
+(default: $FP6M_REFERENCE_DIR, else the directory "reference" beside this repository)
 """
 from __future__ import annotations
 
@@ -19,7 +20,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT_LIB = os.path.join(OUT_DIR, "libfp6ref.so")
-DEFAULT_REFERENCE = os.environ.get("FP6M_REFERENCE_DIR", "/root/reference")
+# the reference checkout: $FP6M_REFERENCE_DIR, else a directory "reference" beside this repository
+DEFAULT_REFERENCE = os.environ.get("FP6M_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 CUDA_INCLUDE = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
 
 
