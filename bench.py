@@ -390,6 +390,86 @@ class LayerBench:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return statistics.median(t.tolist())
 
+    def time_e2e_pipelined(self, steps, min_ms=200.0):
+        """One GPU: the serving loop around the public `mul` with HOST buffers, software-pipelined over three
+        streams and two device buffers: the host->device copy of step i + 1 and the device->host copy of step
+        i - 1 overlap the GEMM of step i.  Every step still copies its A from pinned host memory and its C back.
+        The `steps` steps are captured in one CUDA graph (copies are memcpy nodes of the graph) and replayed;
+        if capture fails the same loop runs eagerly.  Returns (ms per step, mode)."""
+        import torch
+        fm = self.env["fm"]
+        dev = self.env["dev"]
+        s_mm = self.stream
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        a_devs = [self.a_dev, torch.empty_like(self.a_dev)]
+        c_devs = [self.c_dev, torch.empty_like(self.c_dev)]
+        c_hosts = [self.c_host, torch.empty_like(self.c_host).pin_memory()]
+
+        def run(n_steps):
+            fork = torch.cuda.Event()
+            fork.record(s_mm)
+            s_in.wait_event(fork)
+            s_out.wait_event(fork)
+            ev_in, ev_mm, ev_out = [None, None], [None, None], [None, None]
+            for i in range(n_steps):
+                b = i & 1
+                with torch.cuda.stream(s_in):
+                    if ev_mm[b] is not None:
+                        s_in.wait_event(ev_mm[b])              # the GEMM of step i - 2 has read this buffer
+                    a_devs[b].copy_(self.a_host, non_blocking=True)
+                    ev_in[b] = torch.cuda.Event()
+                    ev_in[b].record(s_in)
+                with torch.cuda.stream(s_mm):
+                    s_mm.wait_event(ev_in[b])
+                    if ev_out[b] is not None:
+                        s_mm.wait_event(ev_out[b])             # the result of step i - 2 has left this buffer
+                    B, sc = self.copies[i % len(self.copies)]
+                    fm.mul(a_devs[b], B, c_devs[b], sc, self.workspace, self.qc_local, group_size=self.gs, layout="b200")
+                    ev_mm[b] = torch.cuda.Event()
+                    ev_mm[b].record(s_mm)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_mm[b])
+                    c_hosts[b].copy_(c_devs[b], non_blocking=True)
+                    ev_out[b] = torch.cuda.Event()
+                    ev_out[b].record(s_out)
+            for e in ev_in + ev_out:                            # join
+                if e is not None:
+                    s_mm.wait_event(e)
+
+        with torch.cuda.stream(s_mm):
+            run(4)
+        torch.cuda.synchronize()
+        mode = "graph of the pipelined steps (memcpy nodes + GEMM), replayed"
+        graph = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s_mm):
+                run(steps)
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:          # noqa: BLE001 - capture of cross-stream copies is an optimisation only
+            sys.stderr.write(f"e2e: graph capture of the pipelined loop failed ({exc}); running it eagerly\n")
+            graph = None
+            mode = "eager pipelined loop"
+            torch.cuda.synchronize()
+        times = []
+        total = 0.0
+        while total < min_ms and len(times) < 200:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(s_mm):
+                e0.record(s_mm)
+                if graph is not None:
+                    graph.replay()
+                else:
+                    run(steps)
+                e1.record(s_mm)
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            total += times[-1]
+        ok = bool(torch.equal(c_hosts[(steps - 1) & 1], c_devs[(steps - 1) & 1].cpu()))
+        del graph
+        return statistics.median(times) / steps, mode, ok
+
     def host_us_per_call(self, calls=2000):
         """Host time to enqueue one mul (Python + ctypes + tensor-map encoding + launch), device kept busy."""
         import torch
@@ -538,6 +618,7 @@ def b200_arm(args):
         exchange_ok = lb.check_exchange(warmup - 1) if lb.exchange is not None else None
         times = lb.time_graph(lambda i: lb.step(i, lb.a_dev), steps, sampler=sampler)
         ms_e2e = lb.time_e2e(steps)
+        e2e_pipe = lb.time_e2e_pipelined(steps) if world == 1 else None
         host_us = lb.host_us_per_call() if world == 1 else None
         if world > 1 and not args.no_multi:
             multi = multi_gpu_extras(env, lb, args, peaks)
@@ -572,6 +653,13 @@ def b200_arm(args):
         "clocks": clocks,
         "device_status": status,
     }
+    if e2e_pipe is not None:
+        # the headline end-to-end number is the pipelined serving loop; the strictly serial loop stays beside it
+        line["e2e"].update({"serial_ms_per_step": ms_e2e, "serial_value": line["e2e"]["value"],
+                            "ms_per_step": e2e_pipe[0], "value": nbytes / (e2e_pipe[0] * 1e-3) / 1e9,
+                            "mode": "host->device copy of step i+1 and device->host copy of step i-1 overlap the GEMM of step i "
+                                    "(three streams, two device buffers); " + e2e_pipe[1],
+                            "result_on_host_matches_device": e2e_pipe[2]})
     if host_us is not None:
         line["e2e"]["host_us_per_mul_call"] = host_us
     if exchange_ok is not None:
