@@ -63,6 +63,7 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true", help="skip the other M values and layer shapes (1 GPU)")
     ap.add_argument("--full-sweep", action="store_true", help="every M of every configuration that fits one GPU")
     ap.add_argument("--no-multi", action="store_true", help="N > 1: skip the extra shapes and the part timings")
+    ap.add_argument("--multi-cfg4", action="store_true", help="N > 1: time the compute-bound layer at M = 8192 also on fewer than 8 GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: all-gather of the output columns fused into the GEMM epilogue as peer stores, or NCCL")
@@ -485,11 +486,17 @@ class LayerBench:
         """Parity of the fused exchange: the same step through the NCCL all-gather + column assembly."""
         import torch
         import torch.distributed as dist
-        shard = self.env["shard"]
+        shard, fm = self.env["shard"], self.env["fm"]
+        # both GEMMs with one issuing thread per accumulator tile: bit-identical from run to run, so the two
+        # paths can be compared for equality
+        before = fm.set_ordered_sums(True)
+        self.barrier()
+        self.step(i, self.a_dev)
         self.gemm_only(i, self.a_dev)
         dist.all_gather_into_tensor(self.gathered, self.c_dev)
         expect = shard.assemble(self.gathered, self.plan)
         torch.cuda.synchronize()
+        fm.set_ordered_sums(before)
         ok = torch.tensor([int(torch.equal(expect, self.exchange.outputs[i % 2]))], device=self.env["dev"])
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         return bool(ok.item())
@@ -726,7 +733,7 @@ def multi_gpu_extras(env, lb, args, peaks):
 
     k, n = synth.LLAMA2_70B["gate_up"]
     out["cfg3_70b_gate_up_m16"] = shape_record("70b_gate_up", k, n, 16, QUANT_COLS, 100, 60.0)
-    if world == 8:
+    if world == 8 or args.multi_cfg4:
         out["cfg4_m8192"] = shape_record("cfg4", 16384, 16384, 8192, QUANT_COLS, 2, 60.0)
     return out
 

@@ -45,7 +45,7 @@ struct DeviceGuard {
 
 // How a GEMM of M rows is cut into launches: kernel, tile of rows, rows per launch, grid.
 struct LaunchPlan {
-  bool wide;        // more than 16 rows: the kernel with scaled operands and tiles of 32..256 rows
+  bool wide;        // more than kTc5MaxRows rows: the kernel with scaled operands and tiles of 128 / 256 rows
   int tile;         // rows of A per MMA tile
   int rows;         // rows of A per launch
   int ctas;         // grid of the first (largest) launch
@@ -143,7 +143,7 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   MulParams p;
   p.geo = make_geometry(K, N, qc, group_size);
   if ((long long)kMaxRowTiles * (p.geo.strips4 + p.geo.strips6) * units_per_strip(p.geo) > 0x3fffffff) return FP6M_ERR_PROB_SHAPE;
-  // up to 16 rows: the kernel with fp32 group scaling; more: the wide kernel, tiles of up to 256 rows,
+  // up to kTc5MaxRows rows: the kernel with fp32 group scaling; more: the wide kernel, tiles of up to 256 rows,
   // up to kMaxRowTiles tiles per launch
   const LaunchPlan lp = plan_launches(M, p.geo, sms);
   const bool wide = lp.wide;

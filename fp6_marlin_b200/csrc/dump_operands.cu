@@ -2,7 +2,7 @@
 // expanders the GEMM kernels themselves use (tc5_common.cuh: exact q - 8 or exact E3M2 value / 4096),
 // times the scale with one fp16 rounding.  A test compares it bit-for-bit with the reference's
 // dequantisation rules (test.py:98 for INT4, weight_prepacking.cpp:199-212 for FP6).  The GEMM for
-// more than 16 rows feeds exactly these values to the tensor cores for group-scaled INT4 columns; in
+// more than 128 rows feeds exactly these values to the tensor cores for group-scaled INT4 columns; in
 // the other cases the kernels feed the unscaled expansion and apply the scale to the fp32 sums.
 #include "device_utils.cuh"
 #include "gemm_params.h"

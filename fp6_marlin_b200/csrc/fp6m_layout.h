@@ -208,7 +208,7 @@ inline void make_schedule(const Geometry& g, int ctas, Schedule* out, int row_ti
   out->bound[ctas] = total_units;
 }
 
-// Moves every inner boundary to a whole block (an even unit): the kernel for up to 16 rows works on
+// Moves every inner boundary to a whole block (an even unit): the kernel for up to 128 rows works on
 // 128-row blocks.  The number of units per strip is even, so strips and the total stay aligned.
 inline void align_schedule_to_blocks(Schedule* s) {
   for (int c = 1; c < s->ctas; ++c) s->bound[c] = (s->bound[c] + 1) & ~1;

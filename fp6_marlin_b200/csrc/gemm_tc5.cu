@@ -1,4 +1,6 @@
-// W(4&6)A16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for up to 16 rows of A.
+// W(4&6)A16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for up to 128 rows of A (instances for
+// 16, 32, 64 and 128 rows; the description below is that of the 16-row instance, the others differ in the
+// numbers of teams, stages and tiles - see the configurations at the end of the file).
 //
 // The product is computed transposed, D[n, m] = sum_k W[k, n] * A[m, k]: the 128 weight columns of
 // a strip are the M dimension of tcgen05.mma (one TMEM lane per weight column), the rows of A are
@@ -43,7 +45,8 @@
 // Rings: 15 weight stages, 6 {operand slot, activation tile, accumulator tile} entries.  Both ring sizes
 // are multiples of the number of teams, so a stage or an entry always belongs to the same team and every
 // waiter of an mbarrier observes each of its phases in turn (a parity wait that skipped a phase would
-// pass early).
+// pass early).  Instances whose tiles are too wide to have one per entry keep fewer tiles than entries: the
+// epilogue zeroes a tile after reading it and hands it to the issuers of the segment that uses it next.
 // The INT4 and the FP6 strips run through separate instantiations of the team loop, so that the
 // hot loop holds the instructions of one format only.
 // Strips shared by several CTAs are reduced without atomics or fences on the data path: partials are
@@ -238,6 +241,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   WaitState ws;
   const int s_first = B0 / kb, blk_first = B0 - s_first * kb;
   const uint64_t policy = make_evict_first_policy();
+  FP6M_TRACE_EVENT(trace, 30, 0);              // the CTA's range is known (first reads of the kernel parameters)
 
   // ---- set-up.  Lane 0 of warp kDeqBase + i initialises the barriers of weight stage i and issues the
   // stage's first copy at once (segment i); other threads initialise the remaining barriers, warp 2
@@ -248,10 +252,14 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       mbar_init(w_full + 8 * st, 1);       // the expect_tx arrival of the weights producer
       mbar_init(w_empty + 8 * st, 128);    // every thread of the team that read the stage has used its words
       mbar_fence_init();
+      FP6M_TRACE_EVENT(trace, 31, st);         // the stage's barriers exist
       if (st < nseg) {
         int s = s_first, blk = blk_first + st;
         while (blk >= kb) { blk -= kb; ++s; }
         const uint32_t bytes = segment_bytes(geo, s), sbytes = segment_scale_bytes(geo, s);
+        const uint8_t* src = p.B + segment_offset(geo, s, blk);
+        FP6M_TRACE_EVENT(trace, 32, st);       // source address and size computed
+        (void)src;
         mbar_arrive_expect_tx(w_full + 8 * st, bytes + sbytes);
         tma_load_1d_stream(smem0 + st * kStageW, p.B + segment_offset(geo, s, blk), bytes, w_full + 8 * st, policy);
         if (sbytes)

@@ -1,6 +1,6 @@
-// W(4&6)A16 GEMM on tcgen05 + TMEM for 65 to 256 rows of A per pass (up to 64 rows: gemm_tc5.cu).
+// W(4&6)A16 GEMM on tcgen05 + TMEM for 129 to 256 rows of A per pass (up to 128 rows: gemm_tc5.cu).
 //
-// As in the kernel for up to 16 rows (gemm_tc5.cu) the product is computed transposed: the 128 weight
+// As in the kernel for up to 128 rows (gemm_tc5.cu) the product is computed transposed: the 128 weight
 // columns of a strip are the M dimension of tcgen05.mma (one TMEM lane per column), the rows of A its
 // N dimension (128 or 256), the dequantised weights the A operand in TENSOR MEMORY.  Differences:
 //   * The INT4 group scale is multiplied into the operand - fp16(q - 8) * s_g with one fp16 rounding,

@@ -1,4 +1,4 @@
-"""In-kernel timeline of the GEMM for up to 64 rows (developer tool; needs a B200).
+"""In-kernel timeline of the GEMM for up to 128 rows (developer tool; needs a B200).
 
 The library built with ``python fp6_marlin_b200/build.py --trace`` records, in two CTAs of every launch,
 {tag, argument, SM clock} events of every warp (csrc/trace.cuh), and the start and end of every CTA of the
@@ -58,7 +58,7 @@ def timeline(k, n, m):
     buf = np.zeros((CTAS_TRACED, WARPS, ENTRIES), dtype=np.uint64)
     rc = read(buf.ctypes.data, buf.nbytes)
     print("trace_read rc", rc, "device status", fm.device_status(dev))
-    teams = 3 if m <= 64 else 2          # dequantiser teams of the kernel instance for m rows
+    teams = 3 if m <= 32 else 2          # dequantiser teams of the kernel instance for m rows
     deq = (2 + 2 * teams + 3) & ~3
     epi = deq + 4 * teams
     for ci in range(CTAS_TRACED):
@@ -69,6 +69,8 @@ def timeline(k, n, m):
         print(f"==== traced CTA #{ci} (cycles since the CTA started)")
         print("set-up: barriers initialised / after the CTA-wide barrier and the grid dependency:",
               [(t, tt) for (t, _, tt) in ev[1] if t in (2, 4)])
+        print("a dequantiser warp during set-up: CTA range known (30) / its stage's barriers initialised (31) / copy source computed (32) / copy issued (1):",
+              [(t, tt) for (t, _, tt) in ev[deq] if t in (30, 31, 32, 1)][:4])
         print("first round of weight copies issued at:", sorted(tt for w in range(deq, min(WARPS, deq + 16)) for (t, _, tt) in ev[w] if t == 1))
         print("weights producer, later copies:", [tt for (t, _, tt) in ev[0] if t == 1][:12], "...")
         iss = {}

@@ -207,7 +207,7 @@ int fp6m_pack_b200_device(const void* q4, const void* c6, const void* s4, const 
 int fp6m_set_launch_overlap(int enable);
 
 /* Process-wide option, off by default; returns the previous setting (a negative argument only queries).
- * The GEMM for up to 16 rows of A normally lets two threads issue the tensor-core instructions of one
+ * The GEMM for up to 128 rows of A normally lets two threads issue the tensor-core instructions of one
  * 128-row block, one per 64-row half, into one accumulator: the hardware may retire the halves in either
  * order, so the last bit of a result can differ between two runs on the same inputs (same products, same
  * fp32 adds, different order).  When on, one thread issues a block's instructions in a fixed order and two
