@@ -51,6 +51,7 @@ SIGNATURES = {
     "fp6m_peer_signal_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]),
     "fp6m_peer_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]),
     "fp6m_set_peer_wait_polls": (ctypes.c_int, [ctypes.c_int]),
+    "fp6m_debug_busy_kernel": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "fp6m_encode_fp6_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]),
     "fp6m_pack_b200_device": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2 + [ctypes.c_int, ctypes.c_void_p]),
     "fp6m_set_launch_overlap": (ctypes.c_int, [ctypes.c_int]),

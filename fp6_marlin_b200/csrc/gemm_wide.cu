@@ -147,6 +147,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         }
         const int cnt = it.count();
         const uint32_t bytes = cnt * unit_bytes;            // consecutive units are contiguous in HBM
+        if (phase == 1 && stage == 0) grid_dependency_wait();   // the first S copies need nobody; from here on the teams must have made room
         mbar_wait_bounded<200>(w_empty + 8 * stage, phase ^ 1, p.status, dead);
         mbar_arrive_expect_tx(w_full + 8 * stage, bytes);
         tma_load_1d_stream(smem_u32(smem) + stage * kStageW, wsrc, bytes, w_full + 8 * stage, policy);
@@ -184,9 +185,11 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     // The whole warp walks the segments and waits; one fixed lane issues, so the commits track its MMAs.
     constexpr int I = C::kIssuers;
     const int mine = warp - 2;
+    // every bounded wait below depends on the activations, which the previous kernel of the stream may still be
+    // writing: start them only when it has completed
+    grid_dependency_wait();
     if (mine == I - 1 && lane == 0) {
       // the tag of this launch's split-K partials is epoch + 1
-      grid_dependency_wait();
       const uint32_t e = read_epoch_and_count(p.epochs, gridDim.x);
       misc[1] = e;
       mbar_arrive(epoch_bar);
@@ -248,6 +251,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     const int quarter = warp & 3;                    // the TMEM lanes this warp may touch
     const int c = quarter * 32 + lane;               // weight column inside the strip
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    grid_dependency_wait();                          // the waits below depend, through the MMAs, on the previous kernel's output
     const uint32_t a_base = lane_base + C::kTmemA;
     const uint32_t d_base = lane_base + C::kTmemD + team * RPT;
     const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16

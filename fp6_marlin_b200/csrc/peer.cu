@@ -97,9 +97,28 @@ __global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* ste
   if (status) atomicExch(status, FP6M_ERR_TIMEOUT);
 }
 
+// Lets the kernels behind it in the stream launch at once (programmatic dependent launch) and then keeps one
+// warp busy for `ns` nanoseconds: a long-running predecessor for tests of the launch overlap.
+__global__ void busy_kernel(unsigned long long ns) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  unsigned long long t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  do {
+    __nanosleep(2000);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  } while (t - t0 < ns);
+}
+
 }  // namespace
 
 extern "C" {
+
+int fp6m_debug_busy_kernel(int milliseconds, int dev, void* stream) {
+  if (milliseconds < 0 || milliseconds > 5000) return FP6M_ERR_BAD_ARG;
+  Guard guard(dev);
+  busy_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((unsigned long long)milliseconds * 1000000ull);
+  return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+}
 
 int fp6m_peer_alloc(size_t bytes, int dev, void** ptr, void* handle64) {
   if (!ptr || !handle64 || bytes == 0) return FP6M_ERR_BAD_ARG;

@@ -188,6 +188,11 @@ int fp6m_peer_wait(const void* flags_local, int n, const int* step_dev, int* sta
 int fp6m_set_peer_wait_polls(int polls);
 /* fp6m_peer_signal followed by fp6m_peer_wait in one launch (flag_arrays[rank] is this rank's own array). */
 int fp6m_peer_signal_wait(void* const* flag_arrays, int n, int rank, int* step_dev, int* status_dev, int dev, void* stream);
+/* Test aid: enqueues a one-warp kernel that lets the kernels behind it launch at once (programmatic dependent
+ * launch) and then stays busy for `milliseconds` (0..5000): a long-running predecessor for a GEMM with launch
+ * overlap on, whose bounded waits must not start before that predecessor has finished.  No counterpart in the
+ * reference. */
+int fp6m_debug_busy_kernel(int milliseconds, int dev, void* stream);
 
 /* Device-side weight preparation.  The reference prepares weights in single-threaded host loops
  * (fp6_marlin/weight_quant.cpp:106-124, fp6_marlin/weight_prepacking.cpp:123-177); these two do the same

@@ -62,3 +62,36 @@ def test_wait_that_runs_out_sets_the_status_word_and_returns():
     fm.set_ordered_sums(ordered)
     assert torch.equal(before, after)
     assert fm.device_status(dev) == 0
+
+
+@pytest.mark.parametrize("m", [16, 96, 300])
+def test_long_predecessor_does_not_run_the_bounded_waits_out(m):
+    """Launch overlap on, and the kernel before the GEMM runs for 2.5 s - longer than the ~1 s bound of the
+    GEMM's own waits - after letting its dependents launch at once.  The GEMM's CTAs are resident all that
+    time; their bounded waits must only start once the predecessor has finished: status 0, same result."""
+    dev = torch.device("cuda:0")
+    lib = _lib.lib
+    k, n, qc, gs = 2048, 2048, 256, 128
+    w = synth.make_layer(k, n, qc, gs, seed=9, keep_dequantized=False).to(dev)
+    a = synth.make_activations(m, k, 9).to(dev)
+    workspace = torch.zeros(n // 128 * 16, dtype=torch.int32, device=dev)
+    ordered = fm.set_ordered_sums(True)
+    overlap = fm.set_launch_overlap(False)
+    try:
+        expect = torch.zeros((m, n), dtype=torch.float16, device=dev)
+        fm.mul(a, w.B, expect, w.s, workspace, qc, group_size=gs, layout="b200")
+        torch.cuda.synchronize()
+        fm.set_launch_overlap(True)
+        c = torch.zeros((m, n), dtype=torch.float16, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        t0 = time.perf_counter()
+        assert lib.fp6m_debug_busy_kernel(2500, dev.index or 0, stream) == _lib.OK
+        fm.mul(a, w.B, c, w.s, workspace, qc, group_size=gs, layout="b200")
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+    finally:
+        fm.set_launch_overlap(overlap)
+        fm.set_ordered_sums(ordered)
+    assert 2.4 < elapsed < 4.0, elapsed
+    assert fm.device_status(dev) == 0
+    assert torch.equal(c, expect)
