@@ -543,6 +543,8 @@ def oracle_subset_error(env, lb, n_cols=64):
 def sweep_record(env, tag, k, n, m, qc, peaks, check=True):
     """Latency / GB/s / TFLOP/s of one shape (graph-timed like `value`) and its oracle check."""
     synth = env["synth"]
+    sys.stderr.write(f"sweep: {tag} K={k} N={n} M={m} qc={qc}\n")
+    sys.stderr.flush()
     lb = LayerBench(env, k, n, m, qc, GROUP, seed=1, weight_on_gpu=True,
                     min_copy_bytes=(300e6 if m < 1024 else 0))     # large M re-streams B per 256 rows anyway
     import torch

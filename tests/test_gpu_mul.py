@@ -262,6 +262,22 @@ def test_wide_tiles_and_passes(m):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m", [12, 24, 60, 100, 200, 600])
+def test_ordered_sums_instances_against_the_oracle(m):
+    """The "ordered sums" instances of both kernels (one issuing thread per accumulator tile) are kernels of their
+    own: every tile width against the oracle, and two runs bit for bit."""
+    previous = fm.set_ordered_sums(True)
+    try:
+        for (k, n, qc, gs) in [(1024, 2048, 256, 128), (2048, 768, -1, 128), (8192, 1024, 256, 128)]:
+            err, c1 = _run(m, k, n, qc, gs, 64, 256, seed=m)
+            assert err <= TOL, (m, k, n, qc, gs, err)
+            _, c2 = _run(m, k, n, qc, gs, 64, 256, seed=m)
+            assert torch.equal(c1, c2), (m, k, n, qc, gs)
+    finally:
+        fm.set_ordered_sums(previous)
+
+
+@pytest.mark.gpu
 def test_wide_one_hot_rows_reproduce_scaled_weights_exactly():
     """With group scales the wide kernel feeds fp16((q - 8) * s_g) to the tensor cores: one-hot rows of A
     must return exactly the oracle's dequantised weights (the fp32 sum has a single term)."""
