@@ -230,7 +230,6 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   const unsigned long long t_launch = global_ns();
 #endif
   launch_dependents();
-  if (tid == 32) prefetch_tensormap(&amap);        // the first activation copy then finds the descriptor cached
   if (nseg <= 0) {                     // no work: still counted, see read_epoch_and_count
     if (tid == 0) {
       grid_dependency_wait();

@@ -37,7 +37,7 @@ namespace {
 
 template <int NT_, int TEAMS_, int ISSUERS_, int STAGES_, int ACT_STAGES_, int RING_>
 struct WideCfg {
-  static constexpr int kIssuers = ISSUERS_;            // MMA issuers: issuer i takes the 64-row units h = i, i + I, ... of every segment
+  static constexpr int kIssuers = ISSUERS_;            // MMA issuers = accumulator tiles
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
   static constexpr int kTeams = TEAMS_;
   static constexpr int kStages = STAGES_;              // weight stages (one segment = up to two units each)
@@ -49,7 +49,7 @@ struct WideCfg {
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves, 1024-byte aligned stages
   static constexpr int kNumBars = 2 * kStages + 2 * kActStages + 2 * kRing + 3;
   static constexpr int kSmemBytes = kStages * kStageW + kActStages * kActUnitBytes + kNumBars * 8 + 64 + 1024;
-  static constexpr int kTmemD = 0, kTmemA = NT;        // the accumulator tile, then operand slots of 64 columns
+  static constexpr int kTmemD = 0, kTmemA = kIssuers * NT;   // the accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
   static constexpr int kSlotWords = NT * kStripCols;
@@ -85,7 +85,6 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   const int ups = units_per_strip(geo);
   const int U0 = p.sched.bound[cta], U1 = p.sched.bound[cta + 1];
   launch_dependents();
-  if (tid == 32) prefetch_tensormap(&amap);        // the first activation copy then finds the descriptor cached
   if (U0 >= U1) {                      // no work: still counted, see read_epoch_and_count
     if (tid == 0) {
       grid_dependency_wait();
@@ -97,17 +96,17 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(w_full + 8 * s, 1);      // the expect_tx arrival of the weights producer
-      mbar_init(w_empty + 8 * s, 128);   // every thread of the team that read the stage has its words in registers
+      mbar_init(w_empty + 8 * s, 4);     // the team that read the stage has its words in registers
     }
     for (int s = 0; s < RA; ++s) {
       mbar_init(a_full + 8 * s, 1);      // the expect_tx arrival of the activations producer
       mbar_init(a_empty + 8 * s, 1);     // tcgen05.commit: the MMAs that read the stage have finished
     }
     for (int r = 0; r < R; ++r) {
-      mbar_init(ready + 8 * r, 128);     // every thread of the segment's team stored its operands into TMEM
-      mbar_init(slot_free + 8 * r, C::kIssuers);   // tcgen05.commit of every issuer: the MMAs that read the slot have finished
+      mbar_init(ready + 8 * r, 4);       // the segment's team stored the operands into TMEM
+      mbar_init(slot_free + 8 * r, 1);   // tcgen05.commit: the MMAs that read the slot have finished
     }
-    mbar_init(slice_done, C::kIssuers);  // tcgen05.commit of every issuer: the accumulator tile holds the whole slice
+    mbar_init(slice_done, C::kIssuers);  // tcgen05.commit of every issuer: the accumulator tiles hold the whole slice
     mbar_init(d_read, 4 * T);            // every dequantiser warp has read its part of the tile back
     mbar_init(epoch_bar, 1);
     mbar_fence_init();
@@ -197,46 +196,46 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     __syncwarp();
     Walk it;
     it.init(U0, U1, ups);
-    int r = 0, sa = 0, slices = 0;
+    int r = 0, sa = 0, slices = 0, turn = 0;
     uint32_t rphase = 0, aphase = 0;
-    // One issuer: its first MMA of a slice overwrites the tile.  Several: they add to the tile side by side (the
-    // order in which the tensor core retires their MMAs is not fixed), so the tile starts out zero - the teams
-    // zero it after reading a slice back, and once at the start.
-    bool first = true;                                // my next MMA is my first of the slice
+    bool first = true;                                // my next MMA is my first of the slice: it overwrites my tile
     constexpr uint32_t kStepDesc = 32 >> 4;            // 16 halves along a 128-byte row
     const uint64_t desc0 = wide_act_desc(smem_u32(act_base));
-    const uint32_t d_tmem = tmem + C::kTmemD;
+    const uint32_t d_tmem = tmem + C::kTmemD + mine * NT;
     while (it.valid()) {
       const int cnt = it.count();
-      mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
-      // phase s of d_read: the tile is free (and zero) for the CTA's slice s
-      if (first) mbar_wait_bounded<40>(d_read, slices & 1, p.status, dead);
+      const bool my_turn = I == 1 || turn == mine;
+      if (my_turn) {
+        mbar_wait_bounded<40>(ready + 8 * r, rphase, p.status, dead);
+        if (first && slices > 0) mbar_wait_bounded<40>(d_read, (slices - 1) & 1, p.status, dead);   // previous slice was read back
+      }
       const uint32_t a_tmem = tmem + C::kTmemA + r * 64;
       for (int h = 0; h < cnt; ++h) {
-        if (I == 1 || (h % I) == mine) {
+        if (my_turn) {
           mbar_wait_bounded<40>(a_full + 8 * sa, aphase, p.status, dead);
           tc_fence_after();
           // the descriptor's low 14 bits hold the address / 16: adding an offset never carries out of them
           const uint64_t desc = desc0 + (uint64_t)(sa * (C::kActUnitBytes >> 4));
           if (lane == 0) {
-            tc_mma_unit<kStepDesc>(d_tmem, a_tmem + h * 32, desc, C::kIdesc, (I == 1 && first && h == 0) ? 0u : 1u);
+            tc_mma_unit<kStepDesc>(d_tmem, a_tmem + h * 32, desc, C::kIdesc, first ? 0u : 1u);
             tc_commit(a_empty + 8 * sa);                  // the stage may be refilled when these MMAs are done
           }
           __syncwarp();
+          first = false;
         }
         if (++sa == RA) { sa = 0; aphase ^= 1; }
       }
-      first = false;
       const bool slice_ends = it.next(cnt) || !it.valid();
-      // An issuer without work at the end of a slice runs ahead; its arrival for slice k must not be counted
+      // An issuer without work in a slice runs ahead; its arrival for slice k must not be counted
       // towards slice k - 1, so it first sees that phase complete.
       if (slice_ends && I > 1 && slices > 0) mbar_wait_bounded<40>(slice_done, (slices - 1) & 1, p.status, dead);
       if (lane == 0) {
-        tc_commit(slot_free + 8 * r);                   // completes when all my MMAs so far have finished
-        if (slice_ends) tc_commit(slice_done);
+        if (my_turn) tc_commit(slot_free + 8 * r);
+        if (slice_ends) tc_commit(slice_done);          // completes when all my MMAs so far have finished
       }
       __syncwarp();
       if (slice_ends) { first = true; ++slices; }
+      if (++turn == I) turn = 0;
       if (++r == R) { r = 0; rphase ^= 1; }
     }
   } else if (warp >= C::kDeqBase) {
@@ -257,15 +256,6 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     const uint32_t lds_lo = c * 32 + 16 * ((c >> 2) & 1);          // words 0..3 of the column; words 4..7 at ^ 16
     const int strip_first = U0 / ups;
     const int row0 = team * RPT;
-    // phase 0 of d_read: the tile is free for the CTA's first slice (and zero, when several issuers add to it)
-    if constexpr (C::kIssuers > 1) {
-#pragma unroll 1
-      for (int m0 = 0; m0 < RPT; m0 += CH) tc_st_zero<CH>(d_base + m0);
-      tc_wait_st();
-      tc_fence_before();
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(d_read);
 
     struct Slice {
       int strip_lin, strip, nq, u0, u1, s_begin, tile_row0;   // strip_lin: the VIRTUAL strip (row tile x strip)
@@ -328,84 +318,55 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       half next_scale = __float2half(1.f);
       if (scaled && n - n0 < nseg) next_scale = __ldg(sp0 + (size_t)(b0 + n - n0) * scale_stride);
 
-      // The packed words of a segment are loaded one iteration ahead: while the TMEM stores of one segment
-      // drain, the team already waits for and loads the words of its next segment of the slice.
-      struct Words { uint4 lo[2], hi[2], two[2]; };
-      auto units_of = [&](int j) { return min(unit1, 2 * (b0 + j) + 2) - max(unit0, 2 * (b0 + j)); };
-      // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
-      auto load_words = [&](int stg, int cnt, Words& w) {
-        const uint8_t* st = smem + stg * kStageW;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (h < cnt) {
-            const uint8_t* su = st + h * unit_bytes;
-            w.lo[h] = *reinterpret_cast<const uint4*>(su + lds_lo);          // words 0..3
-            w.hi[h] = *reinterpret_cast<const uint4*>(su + (lds_lo ^ 16));   // words 4..7
-            if (is6) w.two[h] = *reinterpret_cast<const uint4*>(su + two_off);
-          }
-        }
-      };
-      auto expand_unit = [&](const uint4& lo, const uint4& hi, const uint4& two, half2 s2, uint32_t at) {
-        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
-        if (is6) {
-#pragma unroll
-          for (int step = 0; step < 4; ++step) {
-            uint32_t regs[8];
-            expand_fp6(words[2 * step], twos[step], 0, regs);
-            expand_fp6(words[2 * step + 1], twos[step], 4, regs + 4);
-            tc_st8(at + step * 8, regs);
-          }
-        } else if (sl.group) {
-#pragma unroll
-          for (int step = 0; step < 4; ++step) {
-            uint32_t regs[8];
-            expand_int4_scaled(words[2 * step], s2, regs);
-            expand_int4_scaled(words[2 * step + 1], s2, regs + 4);
-            tc_st8(at + step * 8, regs);
-          }
-        } else {
-#pragma unroll
-          for (int step = 0; step < 4; ++step) {
-            uint32_t regs[8];
-            expand_int4(words[2 * step], regs);
-            expand_int4(words[2 * step + 1], regs + 4);
-            tc_st8(at + step * 8, regs);
-          }
-        }
-      };
-      Words w;
-      w.two[0] = w.two[1] = make_uint4(0, 0, 0, 0);
-      if (n - n0 < nseg) {
-        mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
-        load_words(stage, units_of(n - n0), w);
-      }
-#pragma unroll 1
       for (int j = n - n0; j < nseg; j += T) {
         const int b = b0 + j;
-        const int cnt = units_of(j);
+        const int cnt = min(unit1, 2 * b + 2) - max(unit0, 2 * b);
         const half2 s2 = __half2half2(next_scale);
         if (scaled && j + T < nseg) next_scale = __ldg(sp0 + (size_t)(b + T) * scale_stride);   // used one iteration later
+        mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
+        const uint8_t* st = smem + stage * kStageW;
         // the MMAs that read this operand slot R segments ago have finished
         mbar_wait_bounded(slot_free + 8 * r, rphase ^ 1, p.status, dead);
         tc_fence_after();
         const uint32_t a_tmem = a_base + r * 64;
-        expand_unit(w.lo[0], w.hi[0], w.two[0], s2, a_tmem);
-        if (cnt > 1) expand_unit(w.lo[1], w.hi[1], w.two[1], s2, a_tmem + 32);
-        mbar_arrive(w_empty + 8 * stage);                         // this thread has its words of the stage
+#pragma unroll 1
+        for (int h = 0; h < cnt; ++h) {
+          // Columns of padded quads read stale bytes of the stage and produce values nobody stores.
+          const uint8_t* su = st + h * unit_bytes;
+          const uint4 lo = *reinterpret_cast<const uint4*>(su + lds_lo);          // words 0..3
+          const uint4 hi = *reinterpret_cast<const uint4*>(su + (lds_lo ^ 16));   // words 4..7
+          uint4 two = make_uint4(0, 0, 0, 0);
+          if (is6) two = *reinterpret_cast<const uint4*>(su + two_off);
+          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          const uint32_t twos[4] = {two.x, two.y, two.z, two.w};
+#pragma unroll
+          for (int step = 0; step < 4; ++step) {
+            uint32_t regs[8];
+            if (is6) {
+              expand_fp6(words[2 * step], twos[step], 0, regs);
+              expand_fp6(words[2 * step + 1], twos[step], 4, regs + 4);
+            } else if (sl.group) {
+              expand_int4_scaled(words[2 * step], s2, regs);
+              expand_int4_scaled(words[2 * step + 1], s2, regs + 4);
+            } else {
+              expand_int4(words[2 * step], regs);
+              expand_int4(words[2 * step + 1], regs + 4);
+            }
+            tc_st8(a_tmem + h * 32 + step * 8, regs);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(w_empty + 8 * stage);          // the stage's words are in registers
+        tc_wait_st();
+        tc_fence_before();
+        if (lane == 0) mbar_arrive(ready + 8 * r);
         n += T;
         stage += T;
         if (stage >= S) { stage -= S; wphase ^= 1; }
-        if (j + T < nseg) {
-          mbar_wait_bounded(w_full + 8 * stage, wphase, p.status, dead);
-          load_words(stage, units_of(j + T), w);
-        }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(ready + 8 * r);
         r += T;
         if (r >= R) { r -= R; rphase ^= 1; }
       }
+      const int n0_slice = n0;
       n0 += nseg;
       u = sl.u1;
 
@@ -425,9 +386,21 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       }
 #pragma unroll 1
       for (int m0 = 0; m0 < RPT; m0 += CH) {
+        // add the issuers' tiles in issuer order; issuer i took the slice's segments j with
+        // (n0_slice + j) % I == i - one that had none keeps a stale tile, which is skipped
         float v[CH];
-        tc_ld_chunk(d_base + m0, v);
-        if constexpr (C::kIssuers > 1) tc_st_zero<CH>(d_base + m0);     // several issuers add to the tile: the next slice starts from zero
+#pragma unroll
+        for (int q = 0; q < CH; ++q) v[q] = 0.f;
+#pragma unroll
+        for (int i = 0; i < C::kIssuers; ++i) {
+          const int first_j = (i - n0_slice % C::kIssuers + C::kIssuers) % C::kIssuers;
+          if (first_j < nseg) {
+            float t[CH];
+            tc_ld_chunk(d_base + i * NT + m0, t);
+#pragma unroll
+            for (int q = 0; q < CH; ++q) v[q] += t[q];
+          }
+        }
         if (whole) {
           store_rows(sl, m0, v, col_scale, writes);
         } else {
@@ -436,10 +409,9 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
             st_relaxed_u64(slot + (m0 + i) * kStripCols, ((unsigned long long)tag << 32) | __float_as_uint(v[i]));
         }
       }
-      if constexpr (C::kIssuers > 1) tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(d_read);            // the MMA issuers may start the next slice in the tile
+      if (lane == 0) mbar_arrive(d_read);            // the MMA issuer may start the next slice in the tile
       if (!whole && sl.u1 == sl.s_begin + ups) {     // last contributor of the strip: reduce it at the end
         reduce_strip = sl.strip_lin;
         reduce_tag = tag;
@@ -497,12 +469,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
 
 // The number of operand slots is a multiple of the number of teams, so a slot always belongs to the same team
 // and every waiter of a barrier sees each of its phases (a parity wait that skipped a phase would pass early).
-// Four teams with one slot each: a team expands its next segment when the MMAs of its previous one are done.
-// Two issuers (one per 64-row unit of a segment): one thread needs ~200 cycles per tcgen05.mma it issues, the
-// tensor pipe 128 for a 128 x 256 x 16 MMA.  With "ordered sums" one issuer: a fixed order of additions.
-// Eight weight stages: two per team, so that a team's next segment is in shared memory when it asks for it.
-using Wide256 = WideCfg<256, 4, 2, 8, 4, 4>;           // 256 + 4 x 64 = 512 TMEM columns; 96 + 128 KB of stages
-using Wide256Ordered = WideCfg<256, 4, 1, 8, 4, 4>;
+using Wide256 = WideCfg<256, 2, 1, 4, 4, 4>;    // 256 + 4 x 64 = 512 TMEM columns
 
 template <class C>
 cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
@@ -631,7 +598,7 @@ size_t wide_scratch_bytes(int ctas, int rows) {
 cudaError_t launch_gemm_wide(const MulParams& p, int tile_rows, cudaStream_t stream) {
   const bool overlap = tc5_get_overlap();
   (void)tile_rows;                     // always 256: up to 128 rows go to the kernel of gemm_tc5.cu
-  return tc5_get_ordered_sums() ? launch_wide<Wide256Ordered>(p, stream, overlap) : launch_wide<Wide256>(p, stream, overlap);
+  return launch_wide<Wide256>(p, stream, overlap);
 }
 
 }  // namespace fp6m

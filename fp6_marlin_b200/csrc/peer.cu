@@ -8,10 +8,6 @@
 
 #include "../../include/fp6m.h"
 
-namespace fp6m {
-bool tc5_get_overlap();      // gemm_tc5.cu: programmatic dependent launch is switched on
-}
-
 namespace {
 
 struct Guard {
@@ -72,9 +68,6 @@ __global__ void signal_wait_kernel(FlagPointers flags, int n, int rank, int* ste
   // the next GEMM of the stream may set itself up and prefetch its weights during the hand-shake; it touches
   // activations, outputs and scratch only after this kernel has completed (its own griddepcontrol.wait)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  // launched as a programmatic dependent itself, this kernel is resident while the GEMM before it drains and
-  // goes on the moment that GEMM's stores are complete and visible
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ int target;
   if (threadIdx.x == 0) {
     target = *step + 1;
@@ -169,16 +162,9 @@ int fp6m_peer_signal_wait(void* const* flag_arrays, int n, int rank, int* step_d
   Guard guard(dev);
   FlagPointers f = {};
   for (int q = 0; q < n; ++q) f.peer[q] = static_cast<int*>(flag_arrays[q]);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(1);
-  cfg.blockDim = dim3(32);
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = fp6m::tc5_get_overlap() ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, signal_wait_kernel, f, n, rank, step_dev, status_dev, g_wait_polls) == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
+  // (launching this kernel as a programmatic dependent of the GEMM was measured: no gain)
+  signal_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, step_dev, status_dev, g_wait_polls);
+  return cudaGetLastError() == cudaSuccess ? FP6M_OK : FP6M_ERR_CUDA;
 }
 
 int fp6m_set_peer_wait_polls(int polls) {

@@ -177,9 +177,6 @@ __device__ __forceinline__ void store_column_rows(const Params& p, int row0, boo
 __device__ __forceinline__ uint64_t wide_act_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
 // k0 is a multiple of 64 halves = 128 bytes, so the copy starts on a 16-byte boundary
 __device__ __forceinline__ void tma_load_act(uint32_t dst, const CUtensorMap* map, int k0, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
