@@ -19,6 +19,9 @@ its latency.
              Llama-2-7B layers at M = 16 and the compute-bound layer K = N = 16384 at M = 1024, each
              with latency, GB/s, TFLOP/s, fractions of the measured peaks and a relative Frobenius error
              of a column subset against the CPU oracle (checker only).
+  fused_epilogue
+             (1 GPU) the Llama-2-7B gate / up projection at M = 16: `mul_fused` with the SiLU * up epilogue against
+             the unfused GEMM followed by torch kernels.
   multi      (N > 1) GEMM alone / exchange alone / fused per step, a Llama-2-70B gate_up shard at M = 16
              and, on 8 GPUs, the compute-bound layer at M = 8192.
   cpu_baseline / --impl reference
@@ -569,6 +572,57 @@ def sweep_record(env, tag, k, n, m, qc, peaks, check=True):
     return rec
 
 
+def fused_record(env, peaks, m=16):
+    """The Llama-2-7B gate / up projection at M rows: one GEMM whose epilogue computes silu(gate) * up on the
+    fp32 sums (`mul_fused`) against the unfused sequence - the same GEMM writing (M, 2I), then silu * up as
+    torch kernels on the interleaved pairs."""
+    import torch
+    import torch.nn.functional as Fn
+    fm, synth, dev = env["fm"], env["synth"], env["dev"]
+    k, n = synth.LLAMA2_7B["gate_up"]
+    inter = n // 2
+    sys.stderr.write(f"sweep: fused gate_up K={k} I={inter} M={m}\n")
+    gen = torch.Generator(device=dev).manual_seed(11)
+    w_gate = (torch.randn((k, inter), generator=gen, device=dev) * 0.02).half()
+    w_up = (torch.randn((k, inter), generator=gen, device=dev) * 0.02).half()
+    w_gate[:, torch.randperm(inter, generator=gen, device=dev)[: QUANT_COLS // 2]] *= 8.0
+    weight, _ = fm.make_gate_up_weight(w_gate, w_up, QUANT_COLS, GROUP, quant_device=dev)
+    per_copy = weight.B.numel() * 4
+    copies = [(weight.B.to(dev).clone(), weight.s.to(dev).clone()) for _ in range(int(300e6 // per_copy) + 1)]
+    a = synth.make_activations(m, k).to(dev)
+    c_fused = torch.zeros((m, inter), dtype=torch.float16, device=dev)
+    c_full = torch.zeros((m, n), dtype=torch.float16, device=dev)
+    c_act = torch.zeros((m, inter), dtype=torch.float16, device=dev)
+    workspace = torch.zeros(max(n // 128 * 16, 64), dtype=torch.int32, device=dev)
+
+    def fused(i):
+        B, sc = copies[i % len(copies)]
+        fm.mul_fused(a, B, c_fused, sc, workspace, QUANT_COLS, epilogue="silu_mul", group_size=GROUP)
+
+    def unfused(i):
+        B, sc = copies[i % len(copies)]
+        fm.mul(a, B, c_full, sc, workspace, QUANT_COLS, group_size=GROUP, layout="b200")
+        pairs = c_full.view(m, inter, 2)
+        torch.mul(Fn.silu(pairs[:, :, 0]), pairs[:, :, 1], out=c_act)
+
+    lb = LayerBench.__new__(LayerBench)          # only its graph timer is used
+    lb.env, lb.world, lb.stream = env, 1, env["stream"]
+    reps = 100
+    with torch.cuda.stream(env["stream"]):
+        for i in range(3):
+            fused(i)
+            unfused(i)
+        torch.cuda.synchronize()
+        same = float((c_fused.float() - c_act.float()).norm() / c_act.float().norm())
+        t_fused = statistics.median(lb.time_graph(fused, reps, min_ms=60.0, max_replays=50)) * 1e3 / reps
+        t_unfused = statistics.median(lb.time_graph(unfused, reps, min_ms=60.0, max_replays=50)) * 1e3 / reps
+    del copies
+    torch.cuda.empty_cache()
+    return {"shape": "7b_gate_up", "M": m, "K": k, "N": n, "qc": QUANT_COLS, "fused_silu_mul_us": round(t_fused, 2),
+            "unfused_gemm_then_torch_silu_mul_us": round(t_unfused, 2),
+            "rel_difference_fused_vs_unfused": float(f"{same:.3e}")}
+
+
 def run_sweep(env, peaks, full=False, only=None):
     synth = env["synth"]
     if only is not None:
@@ -684,6 +738,7 @@ def b200_arm(args):
     if world == 1 and not args.no_sweep:
         with torch.cuda.stream(env["stream"]):
             line["sweep"] = run_sweep(env, peaks, full=args.full_sweep)
+        line["fused_epilogue"] = fused_record(env, peaks)
         line["device_status"] = line["device_status"] or fm.device_status(dev)
     if rank == 0:
         print(json.dumps(line), flush=True)
