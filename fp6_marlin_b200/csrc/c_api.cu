@@ -159,6 +159,14 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   p.out = out;
   p.epilogue = epilogue;
   p.R = nullptr;
+  {
+    // 16-byte stores of finished rows need every row start and both column bases on 16-byte boundaries
+    const int ld = out.n_out ? out.ld : N;
+    const int base4 = out.n_out ? out.col4 : 0, base6 = out.n_out ? out.col6 : N - qc;
+    bool ok = epilogue == kEpilogueNone && ld % 8 == 0 && base4 % 8 == 0 && base6 % 8 == 0;
+    for (int q = 0; q < out.n_out; ++q) ok = ok && aligned16(out.peer[q]);
+    p.vec_rows = ok ? 1 : 0;
+  }
 
   for (int m0 = 0; m0 < M; m0 += rows) {
     p.A = static_cast<const half*>(A) + (size_t)m0 * K;

@@ -48,7 +48,8 @@ struct WideCfg {
   static constexpr int kDequantThreads = 128 * kTeams;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves, 1024-byte aligned stages
   static constexpr int kNumBars = 2 * kStages + 2 * kActStages + 2 * kRing + 3;
-  static constexpr int kSmemBytes = kStages * kStageW + kActStages * kActUnitBytes + kNumBars * 8 + 64 + 1024;
+  static constexpr int kOutStageBytes = 16 * kStripCols * 2;      // per team: 16 finished rows of a strip in fp16
+  static constexpr int kSmemBytes = kStages * kStageW + kActStages * kActUnitBytes + kTeams * kOutStageBytes + kNumBars * 8 + 64 + 1024;
   static constexpr int kTmemD = 0, kTmemA = kIssuers * NT;   // the accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
@@ -72,7 +73,8 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* act_base = smem + S * kStageW;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(act_base + RA * C::kActUnitBytes);
+  uint8_t* out_stage = act_base + RA * C::kActUnitBytes;            // [team][16 rows][128 columns] fp16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + T * C::kOutStageBytes);
   uint32_t* misc = reinterpret_cast<uint32_t*>(bars + C::kNumBars);   // [0] TMEM base, [1] launch epoch
   const uint32_t w_full = smem_u32(bars), w_empty = w_full + 8 * S;
   const uint32_t a_full = w_empty + 8 * S, a_empty = a_full + 8 * RA;
@@ -289,11 +291,47 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
       const int cc_first = p.sched.bound[cc] / ups;
       return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotWords + row0 * kStripCols + c;
     };
+    // CH finished rows of this thread's column.  Plain path: one 2-byte store per value (a warp writes 64
+    // bytes of a row).  With p.vec_rows the team turns the CH x 128 block round through shared memory and
+    // every thread stores 16 bytes of a row - to C, or to every rank's output over NVLink, where the size of
+    // a write matters most.  All 128 threads of the team call this together.
+    const uint32_t my_stage = smem_u32(out_stage) + team * C::kOutStageBytes;
+    const int team_tid = (warp - C::kDeqBase - 4 * team) * 32 + lane;
     auto store_rows = [&](const Slice& sl, int m0, const float (&v)[CH], float col_scale, bool writes) {
       float out[CH];
 #pragma unroll
       for (int i = 0; i < CH; ++i) out[i] = v[i] * col_scale;
-      store_column_rows<CH>(p, sl.tile_row0 + row0 + m0, sl.is6, sl.strip * kStripCols + c, out, writes);
+      if (!p.vec_rows || CH != 16) {
+        store_column_rows<CH>(p, sl.tile_row0 + row0 + m0, sl.is6, sl.strip * kStripCols + c, out, writes);
+        return;
+      }
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const unsigned short hbits = __half_as_ushort(__float2half_rn(out[i]));
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(my_stage + (uint32_t)(i * kStripCols + c) * 2), "h"(hbits) : "memory");
+      }
+      named_bar_sync(1 + team, 128);
+      const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      const int g = team_tid & 15;                     // eight columns of the strip
+      const int col = sl.strip * kStripCols + g * 8;   // inside the shard's INT4 or FP6 region
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int i = (team_tid >> 4) + 8 * rr;
+        const int row = sl.tile_row0 + row0 + m0 + i;
+        if (row < p.M && g * 8 < ncols) {
+          uint4 val;
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                       : "r"(my_stage + (uint32_t)(i * kStripCols + g * 8) * 2));
+          if (p.out.n_out == 0) {
+            *reinterpret_cast<uint4*>(p.C + (size_t)row * p.N + (sl.is6 ? geo.n4 : 0) + col) = val;
+          } else {
+            const size_t at = (size_t)row * p.out.ld + (sl.is6 ? p.out.col6 : p.out.col4) + col;
+#pragma unroll 1
+            for (int q = 0; q < p.out.n_out; ++q) *reinterpret_cast<uint4*>(p.out.peer[q] + at) = val;
+          }
+        }
+      }
+      named_bar_sync(1 + team, 128);                   // the stage is reused by the next block of rows
     };
 
     int reduce_strip = -1;                           // strip this CTA must reduce at its end

@@ -355,31 +355,43 @@ def test_gpu_fp6_cast_matches_host_on_every_in_range_half():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("m", [16, 48])
-def test_mul_scatter_places_a_shard_in_full_width_outputs(m):
+@pytest.mark.parametrize("m,k,n,qc,n_total,col4,col6", [
+    (16, 512, 512, 128, 2048, 384, 1536 + 128),
+    (48, 512, 512, 128, 2048, 384, 1536 + 128),
+    (300, 512, 512, 128, 2048, 384, 1536 + 128),      # the kernel for more than 128 rows, 16-byte row stores
+    (300, 512, 512, 128, 2048, 388, 1536 + 132),      # column bases off the 16-byte grid: 2-byte stores
+    (200, 1024, 1248 + 32, 32, 4096, 1248, 3000),     # ragged strips (9.75 INT4 strips, 32 FP6 columns)
+    (1100, 16384, 256, 64, 512, 64, 320),             # K = 16384: two launches of 1024 rows with a ragged tail
+])
+def test_mul_scatter_places_a_shard_in_full_width_outputs(m, k, n, qc, n_total, col4, col6):
     """fp6m_mul_scatter (the GEMM whose epilogue is the all-gather): with two local buffers standing in for two
     ranks' outputs, the shard's INT4 and FP6 columns land at their places among the layer's columns and the
     values are those of the plain GEMM."""
     import ctypes
     from fp6_marlin_b200 import _lib, api
     dev = _dev()
-    k, n, qc, gs = 512, 512, 128, 128
-    n_total, col4, col6 = 2048, 384, 1536 + 128
+    gs = 128
     w = synth.make_weight_fp16(k, n, qc, seed=11)
     ww = fm.make_w46_weight(w, qc, gs, keep_dequantized=False).to(dev)
     a = synth.make_activations(m, k, 11).to(dev)
     c = torch.zeros((m, n), dtype=torch.float16, device=dev)
-    workspace = torch.zeros(64, dtype=torch.int32, device=dev)
-    fm.mul(a, ww.B, c, ww.s, workspace, qc, group_size=gs, layout="b200")
-    outs = [torch.full((m, n_total), -7.0, dtype=torch.float16, device=dev) for _ in range(2)]
-    table = (ctypes.c_void_p * 2)(*[o.data_ptr() for o in outs])
-    _, scratch, status = api._device_buffers(dev, (m, n, k, qc))
-    rc = _lib.lib.fp6m_mul_scatter(a.data_ptr(), ww.B.data_ptr(), table, 2, n_total, col4, col6, ww.s.data_ptr(), m, n, k,
-                                   workspace.data_ptr(), workspace.numel() * 4, scratch.data_ptr(), scratch.numel(), dev.index or 0,
-                                   torch.cuda.current_stream(dev).cuda_stream, -1, -1, -1, 16, qc, gs, _lib.LAYOUT_B200,
-                                   status.data_ptr())
-    assert rc == _lib.OK
-    torch.cuda.synchronize()
+    workspace = torch.zeros(max(n // 128 * 16, 64), dtype=torch.int32, device=dev)
+    ordered = fm.set_ordered_sums(True)          # both GEMMs add in one fixed order: comparable bit for bit
+    try:
+        fm.mul(a, ww.B, c, ww.s, workspace, qc, group_size=gs, layout="b200")
+        outs = [torch.full((m, n_total), -7.0, dtype=torch.float16, device=dev) for _ in range(2)]
+        table = (ctypes.c_void_p * 2)(*[o.data_ptr() for o in outs])
+        _, scratch, status = api._device_buffers(dev, (m, n, k, qc))
+        rc = _lib.lib.fp6m_mul_scatter(a.data_ptr(), ww.B.data_ptr(), table, 2, n_total, col4, col6, ww.s.data_ptr(), m, n, k,
+                                       workspace.data_ptr(), workspace.numel() * 4, scratch.data_ptr(), scratch.numel(), dev.index or 0,
+                                       torch.cuda.current_stream(dev).cuda_stream, -1, -1, -1, 16, qc, gs, _lib.LAYOUT_B200,
+                                       status.data_ptr())
+        assert rc == _lib.OK
+        torch.cuda.synchronize()
+    finally:
+        fm.set_ordered_sums(ordered)
+    c_ref = F.gemm_reference(a.cpu().numpy(), _oracle_weight(w, qc, gs))
+    assert F.rel_frobenius(c.cpu().numpy().astype(np.float32), c_ref) <= TOL
     for o in outs:
         assert torch.equal(o[:, col4:col4 + n - qc], c[:, : n - qc])
         assert torch.equal(o[:, col6:col6 + qc], c[:, n - qc:])
