@@ -71,6 +71,7 @@ cudaError_t launch_gemm_tc5(const MulParams& p, cudaStream_t stream);
 // gemm_wide.cu
 cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUtensorMap* map);
 cudaError_t encode_activation_segment_map(const half* A, int M, int K, int box_rows, CUtensorMap* map);
+cudaError_t encode_output_map(const half* base, int rows, int ld, CUtensorMap* map);
 constexpr int kMaxWideCtas = 192;   // one CTA per SM
 constexpr int kMaxRowTiles = 32;    // 8192 rows of A per launch
 int wide_rows_per_pass();

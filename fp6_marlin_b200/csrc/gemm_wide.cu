@@ -48,7 +48,7 @@ struct WideCfg {
   static constexpr int kDequantThreads = 128 * kTeams;
   static constexpr int kActUnitBytes = NT * 128;       // NT rows x 64 halves, 1024-byte aligned stages
   static constexpr int kNumBars = 2 * kStages + 2 * kActStages + 2 * kRing + 3;
-  static constexpr int kOutStageBytes = 16 * kStripCols * 2;      // per team: 16 finished rows of a strip in fp16
+  static constexpr int kOutStageBytes = 2 * 16 * kStripCols * 2;  // per team: two buffers of 16 finished rows of a strip in fp16
   static constexpr int kSmemBytes = kStages * kStageW + kActStages * kActUnitBytes + kTeams * kOutStageBytes + kNumBars * 8 + 64 + 1024;
   static constexpr int kTmemD = 0, kTmemA = kIssuers * NT;   // the accumulator tiles, then operand slots of 64 columns
   static constexpr int kTmemUsed = kTmemA + kRing * 64;
@@ -66,9 +66,22 @@ __device__ __forceinline__ void tma_load_act_rows(uint32_t dst, const CUtensorMa
                ::"r"(dst), "l"(map), "r"(k0), "r"(row0), "r"(bar) : "memory");
 }
 
+// Tensor maps of the outputs (C, or every rank's full-width output) for the asynchronous row stores; box = 128
+// columns x 16 rows.  Only read when p.vec_rows == 2.
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
+// 16 rows x 128 columns of fp16 from shared memory (row-major, 256 bytes per row) to the output behind `map` at
+// column x (a multiple of 8), row y; rows beyond the output's last row are clipped by the copy engine.
+__device__ __forceinline__ void tma_store_rows(const CUtensorMap* map, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(src_smem) : "memory");
+}
+
 template <class C>
 __global__ void __launch_bounds__(C::kThreads, 1)
-w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant__ CUtensorMap amap) {
+w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant__ CUtensorMap amap, const __grid_constant__ OutMaps omaps) {
   constexpr int NT = C::NT, S = C::kStages, RA = C::kActStages, R = C::kRing, T = C::kTeams;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -297,6 +310,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
     // a write matters most.  All 128 threads of the team call this together.
     const uint32_t my_stage = smem_u32(out_stage) + team * C::kOutStageBytes;
     const int team_tid = (warp - C::kDeqBase - 4 * team) * 32 + lane;
+    int stage_turn = 0;                                // which of the team's two buffers the next block of rows uses
     auto store_rows = [&](const Slice& sl, int m0, const float (&v)[CH], float col_scale, bool writes) {
       float out[CH];
 #pragma unroll
@@ -305,33 +319,55 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         store_column_rows<CH>(p, sl.tile_row0 + row0 + m0, sl.is6, sl.strip * kStripCols + c, out, writes);
         return;
       }
+      const uint32_t buf = my_stage + (uint32_t)(stage_turn & 1) * (16 * kStripCols * 2);
+      ++stage_turn;
+      // the copy engine has read the rows this buffer held two blocks ago (only team thread 0 issues copies)
+      if (team_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      named_bar_sync(1 + team, 128);
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const unsigned short hbits = __half_as_ushort(__float2half_rn(out[i]));
-        asm volatile("st.shared.u16 [%0], %1;" ::"r"(my_stage + (uint32_t)(i * kStripCols + c) * 2), "h"(hbits) : "memory");
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(buf + (uint32_t)(i * kStripCols + c) * 2), "h"(hbits) : "memory");
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the copy engine reads what this thread wrote
       named_bar_sync(1 + team, 128);
       const int ncols = strip_cols(sl.is6 ? geo.n6 : geo.n4, sl.strip);
+      const int row_first = sl.tile_row0 + row0 + m0;
+      if (row_first >= p.M) return;                    // uniform over the team
+      const int col_strip = (p.out.n_out == 0 ? (sl.is6 ? geo.n4 : 0) : (sl.is6 ? p.out.col6 : p.out.col4)) + sl.strip * kStripCols;
+      if (p.vec_rows == 2 && ncols == kStripCols) {
+        // a full strip: one asynchronous tensor store per output; the team goes on at once
+        if (team_tid == 0) {
+          const int n_maps = p.out.n_out == 0 ? 1 : p.out.n_out;
+#pragma unroll 1
+          for (int q = 0; q < n_maps; ++q) tma_store_rows(&omaps.m[q], buf, col_strip, row_first);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        return;
+      }
       const int g = team_tid & 15;                     // eight columns of the strip
-      const int col = sl.strip * kStripCols + g * 8;   // inside the shard's INT4 or FP6 region
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         const int i = (team_tid >> 4) + 8 * rr;
-        const int row = sl.tile_row0 + row0 + m0 + i;
+        const int row = row_first + i;
         if (row < p.M && g * 8 < ncols) {
           uint4 val;
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
-                       : "r"(my_stage + (uint32_t)(i * kStripCols + g * 8) * 2));
+                       : "r"(buf + (uint32_t)(i * kStripCols + g * 8) * 2));
           if (p.out.n_out == 0) {
-            *reinterpret_cast<uint4*>(p.C + (size_t)row * p.N + (sl.is6 ? geo.n4 : 0) + col) = val;
+            *reinterpret_cast<uint4*>(p.C + (size_t)row * p.N + col_strip + g * 8) = val;
           } else {
-            const size_t at = (size_t)row * p.out.ld + (sl.is6 ? p.out.col6 : p.out.col4) + col;
+            const size_t at = (size_t)row * p.out.ld + col_strip + g * 8;
 #pragma unroll 1
             for (int q = 0; q < p.out.n_out; ++q) *reinterpret_cast<uint4*>(p.out.peer[q] + at) = val;
           }
         }
       }
-      named_bar_sync(1 + team, 128);                   // the stage is reused by the next block of rows
+      // (the buffer is not written again before the barrier at the top of the block after next)
+    };
+    // before the team leaves: its asynchronous stores have been performed
+    auto drain_stores = [&]() {
+      if (team_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     };
 
     int reduce_strip = -1;                           // strip this CTA must reduce at its end
@@ -495,6 +531,7 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         store_rows(sl, m0, sum, col_scale, writes);
       }
     }
+    drain_stores();
   }
 
   // ---- all roles are done with tensor memory: give it back
@@ -510,10 +547,22 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
 using Wide256 = WideCfg<256, 2, 1, 4, 4, 4>;    // 256 + 4 x 64 = 512 TMEM columns
 
 template <class C>
-cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
+cudaError_t launch_wide(const MulParams& p_in, cudaStream_t stream, bool overlap) {
   alignas(64) CUtensorMap amap;
-  cudaError_t me = encode_activation_map(p.A, p.M, p.K, C::NT, &amap);
+  cudaError_t me = encode_activation_map(p_in.A, p_in.M, p_in.K, C::NT, &amap);
   if (me != cudaSuccess) return me;
+  MulParams p = p_in;
+  alignas(64) OutMaps omaps = {};
+  if (p.vec_rows) {
+    // asynchronous tensor stores of the finished rows: one map per output; without them the 16-byte stores stay
+    bool ok = true;
+    if (p.out.n_out == 0) {
+      ok = encode_output_map(p.C, p.M, p.N, &omaps.m[0]) == cudaSuccess;
+    } else {
+      for (int q = 0; q < p.out.n_out && ok; ++q) ok = encode_output_map(p.out.peer[q], p.M, p.out.ld, &omaps.m[q]) == cudaSuccess;
+    }
+    if (ok) p.vec_rows = 2;
+  }
 
   static bool configured[64] = {};
   int dev = 0;
@@ -533,7 +582,7 @@ cudaError_t launch_wide(const MulParams& p, cudaStream_t stream, bool overlap) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, w46_gemm_wide_kernel<C>, p, amap);
+  return cudaLaunchKernelEx(&cfg, w46_gemm_wide_kernel<C>, p, amap, omaps);
 }
 
 }  // namespace
@@ -565,7 +614,7 @@ struct MapKey {
   int M, K, box_rows, dims;
 };
 struct MapCache {
-  static constexpr int kEntries = 8;
+  static constexpr int kEntries = 96;      // a GEMM of many launches onto eight outputs has 64 output maps
   MapKey key[kEntries] = {};
   CUtensorMap map[kEntries];
   int next = 0;
@@ -599,6 +648,24 @@ cudaError_t encode_activation_map(const half* A, int M, int K, int box_rows, CUt
   const cuuint32_t elem[2] = {1, 1};
   if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  g_map_cache.put(mk, *map);
+  return cudaSuccess;
+}
+
+// An output (C, or a rank's full-width output) as an `ld` x `rows` fp16 tensor; one box = 128 columns x 16 rows,
+// row-major in shared memory (no swizzle).  Stores beyond the last row are clipped.
+cudaError_t encode_output_map(const half* base, int rows, int ld, CUtensorMap* map) {
+  const MapKey mk = {base, rows, ld, 16, 4};
+  if (g_map_cache.find(mk, map)) return cudaSuccess;
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kStripCols, 16};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
   g_map_cache.put(mk, *map);
   return cudaSuccess;
