@@ -774,22 +774,14 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
 #endif
 using Tc5Rows16 = Tc5Cfg<16, FP6M_TC5_STAGES, 2 * FP6M_TC5_TEAMS, FP6M_TC5_TEAMS, true>;          // 3 teams: 6 x 16 + 6 x 64 = 480 TMEM columns
 using Tc5Rows16Ordered = Tc5Cfg<16, FP6M_TC5_STAGES, 2 * FP6M_TC5_TEAMS, FP6M_TC5_TEAMS, false>;  // one issuing thread per accumulator tile: run-to-run bit-identical
-// 17 to 64 rows: the tiles are too wide for six of them: two accumulator tiles (2 x 32 or 2 x 64 TMEM columns)
-// beside the six operand slots; the activation tiles grow with the rows, the weight stages give way
-#ifndef FP6M_TC5_WIDE_CFG
-#define FP6M_TC5_WIDE_CFG 1
-#endif
-#if FP6M_TC5_WIDE_CFG
+// 17 to 32 rows: three teams and six operand slots as above, four accumulator tiles of 32 TMEM columns.
+// 33 to 64 rows: two teams, four operand slots and four accumulator tiles of 64 columns (with six slots only two
+// tiles fit, and the chain MMA -> read-back -> next MMA on two tiles is as slow as two teams).
+// The activation tiles grow with the rows, the weight stages give way.
 using Tc5Rows32 = Tc5Cfg<32, 12, 6, 3, true, 4>;
 using Tc5Rows32Ordered = Tc5Cfg<32, 12, 6, 3, false, 4>;
 using Tc5Rows64 = Tc5Cfg<64, 10, 4, 2, true>;
 using Tc5Rows64Ordered = Tc5Cfg<64, 10, 4, 2, false>;
-#else
-using Tc5Rows32 = Tc5Cfg<32, 14, 4, 2, true>;
-using Tc5Rows32Ordered = Tc5Cfg<32, 14, 4, 2, false>;
-using Tc5Rows64 = Tc5Cfg<64, 10, 4, 2, true>;
-using Tc5Rows64Ordered = Tc5Cfg<64, 10, 4, 2, false>;
-#endif
 
 // 65 to 128 rows: two teams, four operand slots (256 TMEM columns) beside two accumulator tiles of 128 columns;
 // four epilogue sets of 32 rows each
