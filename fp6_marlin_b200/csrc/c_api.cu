@@ -57,8 +57,10 @@ LaunchPlan plan_launches(int M, const Geometry& geo, int sms) {
   lp.wide = M > kTc5MaxRows;
   lp.tile = lp.wide ? wide_tile_rows(M) : tc5_tile_rows(M);
   // CTAs own contiguous ranges of (tile, strip) pairs, so the tiles of a launch are all in flight at once:
-  // keep their activations (tile x K halves each) within a quarter of L2
-  int max_tiles = (int)((32ll << 20) / ((long long)lp.tile * geo.K * 2));
+  // keep their activations (tile x K halves each) within half of L2
+  // (measured at K = 16384: 64 MB of activations per launch are as fast as 32 MB on a full layer and 23 % faster
+  // on a shard of 2048 columns, whose 16 strips need eight row tiles to give every CTA a strip; 96 MB are slower)
+  int max_tiles = (int)((64ll << 20) / ((long long)lp.tile * geo.K * 2));
   if (max_tiles < 1) max_tiles = 1;
   if (max_tiles > kMaxRowTiles) max_tiles = kMaxRowTiles;
   lp.rows = lp.wide ? lp.tile * max_tiles : lp.tile;

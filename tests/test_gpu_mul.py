@@ -361,7 +361,7 @@ def test_gpu_fp6_cast_matches_host_on_every_in_range_half():
     (300, 512, 512, 128, 2048, 384, 1536 + 128),      # the kernel for more than 128 rows, 16-byte row stores
     (300, 512, 512, 128, 2048, 388, 1536 + 132),      # column bases off the 16-byte grid: 2-byte stores
     (200, 1024, 1248 + 32, 32, 4096, 1248, 3000),     # ragged strips (9.75 INT4 strips, 32 FP6 columns)
-    (1100, 16384, 256, 64, 512, 64, 320),             # K = 16384: two launches of 1024 rows with a ragged tail
+    (2300, 16384, 256, 64, 512, 64, 320),             # K = 16384: two launches (2048 rows and a ragged tail)
 ])
 def test_mul_scatter_places_a_shard_in_full_width_outputs(m, k, n, qc, n_total, col4, col6):
     """fp6m_mul_scatter (the GEMM whose epilogue is the all-gather): with two local buffers standing in for two

@@ -52,17 +52,18 @@ def _mul(a, ww, m, n, qc, gs, dev):
 
 @pytest.mark.parametrize("qc", [0, 128, 256, 512])
 def test_compute_bound_geometry_with_several_launches(qc):
-    """K = 16384: one launch covers 1024 rows of A, so M = 2304 is three launches with a ragged last one and
-    M = 4096 is four.  Checked on a subset of rows that touches every launch and every 256-row tile edge."""
+    """K = 16384: one launch covers 2048 rows of A (eight 256-row tiles), so M = 2304 is two launches with a ragged
+    last one, M = 4096 two full ones and M = 4400 three.  Checked on a subset of rows that touches every launch and
+    256-row tile edges."""
     dev = _dev()
     k, n, gs = 16384, 1024, 128
     w = synth.make_weight_fp16(k, n, qc, seed=40 + qc)
     ww = fm.make_w46_weight(w, qc if qc else -1, gs, keep_dequantized=False).to(dev)
     w_deq = _oracle_weight(w, qc, gs)
-    for m in (1024, 2304, 4096):
+    for m in (1024, 2304, 4096, 4400):
         a = synth.make_activations(m, k, seed=m)
         c = _mul(a.to(dev), ww, m, n, qc if qc else -1, gs, dev).cpu().numpy().astype(np.float32)
-        rows = sorted({0, 1, 255, 256, 511, 1023, 1024 % m, 1025 % m, 2047 % m, 2048 % m, 2303 % m, m - 257, m - 2, m - 1})
+        rows = sorted({0, 1, 255, 256, 511, 1023, 1024 % m, 1025 % m, 2047 % m, 2048 % m, 2303 % m, 4095 % m, 4096 % m, m - 257, m - 2, m - 1})
         c_ref = F.gemm_reference(a.numpy()[rows], w_deq)
         err = F.rel_frobenius(c[rows], c_ref)
         assert err <= TOL, (qc, m, err)
