@@ -310,7 +310,9 @@ class LayerBench:
             dist.all_gather_into_tensor(self.gathered, self.c_dev)
 
     def launches_per_step(self):
-        per_gemm = max(1, -(-self.m // 1024)) if self.m > 16 else 1
+        # up to 128 rows: one launch; more: launches of up to min(32, 64 MB / (256 K 2 B)) tiles of 256 rows
+        rows_per_launch = 256 * max(1, min(32, (64 << 20) // (256 * self.k * 2)))
+        per_gemm = 1 if self.m <= 128 else -(-self.m // rows_per_launch)
         return per_gemm + (1 if self.exchange is not None else 0)
 
     # ---- timing
