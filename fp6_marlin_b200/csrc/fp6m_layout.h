@@ -129,7 +129,7 @@ FP6M_HD int int4_nibble_pos(int i) { return (i & 1) ? 4 + (i >> 1) : (i >> 1); }
 
 // ---------------------------------------------------------------------------------------------
 // Stripe schedule.  Units are ordered strip-major (INT4 strips, then FP6 strips), rows fastest,
-// and weighted by their cost (unit_cost: 8 per INT4 unit, 9 per FP6 unit).  CTA c owns the units
+// and weighted by their cost (unit_cost: 8 per INT4 unit, 11 per FP6 unit).  CTA c owns the units
 // [bound[c], bound[c+1]); a strip that is shared by several CTAs is reduced in fp32 by the last
 // of them to finish.  Replaces the reference's static INT4/FP6 SM split and its stripe
 // arithmetic (fp6_marlin_cuda_kernel.cu:308-408).
@@ -141,11 +141,14 @@ struct Schedule {
 };
 
 // Cost of one unit for the schedule.  The kernels are bound by per-unit instruction work, which does
-// not depend on how many of the strip's 128 columns exist and is only slightly larger for FP6 than
-// for INT4 (measured: CTAs given FP6 units by their byte count finished in half the time).
+// not depend on how many of the strip's 128 columns exist and is larger for FP6 than for INT4, but by less
+// than the byte count (measured: CTAs given FP6 units by their byte count, 12 : 8, finished early; with 9 : 8
+// the few CTAs that hold the FP6 strips finished last and every step waited a microsecond for them; 10.5 to
+// 12 : 8 are equal within the noise).
+constexpr int kInt4UnitCost = 8, kFp6UnitCost = 11;
 FP6M_HD int unit_cost(const Geometry& g, int strip_linear) {
   // with several row tiles per launch the strips repeat (virtual strip = tile * strips + strip)
-  return strip_linear % (g.strips4 + g.strips6) < g.strips4 ? 8 : 9;
+  return strip_linear % (g.strips4 + g.strips6) < g.strips4 ? kInt4UnitCost : kFp6UnitCost;
 }
 
 // First unit u in [u0, u1] such that the weight of [u0, u) is >= target (u1 if never).
@@ -187,25 +190,48 @@ inline void make_schedule(const Geometry& g, int ctas, Schedule* out, int row_ti
   const int ups = units_per_strip(g);
   const int nstrips = g.strips4 + g.strips6;
   const int total_units = row_tiles * nstrips * ups;
-  const long long total_cost = (long long)row_tiles * ups * (8ll * g.strips4 + 9ll * g.strips6);
+  const long long total_cost = (long long)row_tiles * ups * ((long long)kInt4UnitCost * g.strips4 + (long long)kFp6UnitCost * g.strips6);
   out->ctas = ctas;
   out->total_units = total_units;
-  // bound[c] = unit_at_cost(g, 0, total_units, total_cost * c / ctas), all of them in one walk over the
-  // strips (the targets rise with c)
-  int strip = 0, real = 0;          // the strip the walk is in; its index among the strips of one row tile
-  long long acc = 0;                // cost of the units before that strip
-  for (int c = 0; c < ctas; ++c) {
-    const long long target = total_cost * c / ctas;
-    int cost = real < g.strips4 ? 8 : 9;
-    while (acc + (long long)ups * cost <= target) {
-      acc += (long long)ups * cost;
-      ++strip;
-      if (++real == nstrips) real = 0;
-      cost = real < g.strips4 ? 8 : 9;
+  // A CTA whose range starts inside a strip and reaches the strip's end reduces that strip at its own end
+  // (the kernel for up to 128 rows): such CTAs get `kReducerPenalty` cost units (one segment) less work than
+  // the others - measured 1 to 2 % on the steps of the Llama-2 layers; two or four segments less are no better.
+  // Which CTAs they are depends on the boundaries, so the shares are settled in a few rounds.
+  constexpr int kReducerPenalty = 16;
+  double share[kMaxCtas];
+  for (int c = 0; c < ctas; ++c) share[c] = 1.0;
+  const int rounds = (kReducerPenalty > 0 && row_tiles == 1) ? 4 : 1;
+  for (int round = 0; round < rounds; ++round) {
+    double share_total = 0.0;
+    for (int c = 0; c < ctas; ++c) share_total += share[c];
+    // bound[c] = first unit at which the cost of the units before it reaches CTA c's target, all of them in
+    // one walk over the strips (the targets rise with c)
+    int strip = 0, real = 0;          // the strip the walk is in; its index among the strips of one row tile
+    long long acc = 0;                // cost of the units before that strip
+    double before = 0.0;
+    for (int c = 0; c < ctas; ++c) {
+      const long long target = rounds == 1 ? total_cost * c / ctas : (long long)((double)total_cost * (before / share_total));
+      before += share[c];
+      int cost = real < g.strips4 ? kInt4UnitCost : kFp6UnitCost;
+      while (acc + (long long)ups * cost <= target) {
+        acc += (long long)ups * cost;
+        ++strip;
+        if (++real == nstrips) real = 0;
+        cost = real < g.strips4 ? kInt4UnitCost : kFp6UnitCost;
+      }
+      out->bound[c] = strip * ups + (int)((target - acc + cost - 1) / cost);
     }
-    out->bound[c] = strip * ups + (int)((target - acc + cost - 1) / cost);
+    out->bound[ctas] = total_units;
+    if (round + 1 < rounds) {
+      const double per_cta = (double)total_cost / ctas;
+      for (int c = 0; c < ctas; ++c) {
+        const int u0 = out->bound[c], u1 = out->bound[c + 1];
+        const bool reduces = (u0 % ups) != 0 && u1 >= (u0 / ups + 1) * ups;
+        share[c] = reduces ? 1.0 - (double)kReducerPenalty / per_cta : 1.0;
+        if (share[c] < 0.25) share[c] = 0.25;
+      }
+    }
   }
-  out->bound[ctas] = total_units;
 }
 
 // Moves every inner boundary to a whole block (an even unit): the kernel for up to 128 rows works on
