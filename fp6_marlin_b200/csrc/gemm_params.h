@@ -47,6 +47,7 @@ struct MulParams {
   unsigned long long* partials;    // split-K slots (scratch): {fp32 value, epoch tag} per 64-bit word
   int* status;          // optional device status word
   OutputMap out;
+  int expand_early;     // kernel for up to 128 rows: the teams expand their first segments before the grid dependency
   int vec_rows;         // kernel for more than 128 rows: finished rows leave as 16-byte stores (every row start and both
                         // column bases are multiples of 8 halves, no fused epilogue)
   Schedule sched;

@@ -286,10 +286,12 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
   tc_fence_after();
   const uint32_t tmem = misc[0];
   // Everything below depends, directly or through the MMAs, on the activations, which the previous
-  // kernel of the stream may still be writing: all bounded waits start after it has completed.
-  // (Letting the dequantiser teams expand their first segments before this wait was measured: no gain
-  // on a chain of GEMMs - a step is as long as the life of the CTAs that start last.)
-  grid_dependency_wait();
+  // kernel of the stream may still be writing: all bounded waits that depend on them start after it has
+  // completed.  With p.expand_early the dequantiser teams go ahead: their first two segments each need the
+  // (static) weights and fresh ring entries only, so their operands are in tensor memory when the activations
+  // arrive (the host switches it on where a CTA's main loop is short against its set-up).
+  const bool is_team_warp = p.expand_early && warp >= C::kDeqBase && warp < C::kEpiBase;
+  if (!is_team_warp) grid_dependency_wait();
   FP6M_TRACE_EVENT(trace, 4, 0);
 
   if (warp == C::kEpochWarp && lane == 0) {
@@ -580,9 +582,15 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       mbar_wait(w_full + 8 * stage, wphase, ws);
       load_words(sp, stage, w);
     }
+    bool after_grid_wait = !p.expand_early;
 #pragma unroll 1
     while (n < nseg) {
       FP6M_TRACE_EVENT(trace, 10, n);
+      if (n >= R && !after_grid_wait) {
+        // from the team's third segment on its waits depend on the MMAs, hence on the previous kernel
+        grid_dependency_wait();
+        after_grid_wait = true;
+      }
       if constexpr (C::kDecoupled) {
         // the MMAs of the segment that used this ring entry before are done
         mbar_wait(done + 8 * r, rphase, ws);
@@ -630,6 +638,7 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       if (r >= R) { r -= R; rphase ^= 1; }
       n = n_next;
     }
+    if (!after_grid_wait) grid_dependency_wait();
     if (C::kEpiSets == 2 && team < 2) reduce_shared_strip(2 + team);     // groups 0 and 1 are the epilogue sets (four sets need no help)
   } else if (warp >= C::kEpiBase) {
     // ================================================================== epilogue
