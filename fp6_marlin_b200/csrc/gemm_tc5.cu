@@ -90,6 +90,12 @@ struct Tc5Cfg {
   static constexpr int kEpiBase = kDeqBase + 4 * kTeams;
   static constexpr int kEpiSets = NT_ > 64 ? 4 : 2;       // a thread of an epilogue set accumulates at most 32 rows
   static constexpr int kThreads = 32 * (kEpiBase + 4 * kEpiSets);
+  // Groups of 128 threads that share the reduction of a strip at the CTA's end.  Four: the epilogue sets, with
+  // the first two teams where there are only two sets.  Eight (128-row tiles, where a strip's partials are 128 KB
+  // per contributor and the reduction is a chain of round trips to L2): the four sets, the two teams and the
+  // eight warps in front of them (producers, issuers, two spare warps), sixteen rows each.
+  // (measured at 128 rows, K = N = 8192: 32.0 -> 27.7 us per GEMM; K = N = 4096: 26.0 -> 19.9)
+  static constexpr int kReduceGroups = (kEpiSets == 4 && kTeams == 2 && kDeqBase == 8) ? 8 : 4;
   static_assert(kTeams >= 2 && STAGES_ <= 4 * kTeams + 4 * kEpiSets, "the first round of weight copies is issued by one warp per stage");
   static constexpr int kEpochWarp = 2 + kIssuers - 1;
   static constexpr int NT = NT_;                       // rows of A per pass = N of the MMA
@@ -356,16 +362,18 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     return p.partials + (size_t)(2 * cc + (strip_lin != cc_first ? 1 : 0)) * C::kSlotFloats + c;
   };
   // After its last segment: the strip whose LAST contributor (in CTA order) this CTA is - the strip its range
-  // starts inside of and runs to the end of.  Four groups of 128 threads take part, each with a quarter of the
-  // rows: the epilogue sets and, where there are only two of those, the first two dequantiser teams (which
-  // have nothing else left to do), so that the tagged words of up to four contributors travel together.  A
+  // starts inside of and runs to the end of.  kReduceGroups groups of 128 threads take part, each with its share
+  // of the rows: the epilogue sets, dequantiser teams (which have nothing else left to do) and, with eight
+  // groups, the warps in front of them, so that many tagged words travel together.  A
   // value is added in CTA order, so the sum does not depend on the timing.  (Measured and dropped: giving
   // all of it to the warps that run out of work first - teams, issuers - ends the reducing CTAs earlier but
   // lengthened the step of the square layer by 4 %.)
   auto reduce_shared_strip = [&](int group) {
     if (!(blk_first > 0 && nseg >= kb - blk_first)) return;         // this CTA is no strip's last contributor
-    constexpr int RR = NT / 4;                                       // rows of this thread
-    constexpr int kInFlight = NT > 64 ? 8 : 16;                      // 64-bit loads in flight per thread (registers)
+    constexpr int RR = NT / C::kReduceGroups;                        // rows of this thread
+    // 64-bit loads in flight per thread: the 128-row instance runs 1024 threads of 64 registers (16 in flight spill
+    // there and are 3 % slower)
+    constexpr int kInFlight = NT > 64 ? 8 : 16;
     constexpr int kChunk = RR < kInFlight ? RR : kInFlight;          // rows per round
     constexpr int kBatch = kInFlight / kChunk;                       // contributors per round
     const int rr0 = group * RR;
@@ -639,7 +647,9 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
       n = n_next;
     }
     if (!after_grid_wait) grid_dependency_wait();
-    if (C::kEpiSets == 2 && team < 2) reduce_shared_strip(2 + team);     // groups 0 and 1 are the epilogue sets (four sets need no help)
+    // groups 0.. are the epilogue sets
+    if (C::kReduceGroups == 8) reduce_shared_strip(4 + team);
+    else if (C::kEpiSets == 2 && team < 2) reduce_shared_strip(2 + team);
   } else if (warp >= C::kEpiBase) {
     // ================================================================== epilogue
     // Two sets of one warp per lane quarter; thread = weight column.  Set e reads the accumulator tiles of
@@ -761,6 +771,12 @@ __global__ void __launch_bounds__(C::kThreads, 1) w46_gemm_tc5_kernel(const __gr
     FP6M_TRACE_EVENT(trace, 23, 0);
   }
 
+  if (C::kReduceGroups == 8 && warp < 8) {
+    // producers, issuers and the spare warps: the four warps of a group go in together, when its issuers are done
+    __syncwarp();
+    named_bar_sync(6 + (warp >> 2), 128);
+    reduce_shared_strip(6 + (warp >> 2));
+  }
   report_waits(ws, p.status);
   // ---- all roles are done with tensor memory: give it back
   tc_fence_before();

@@ -358,6 +358,10 @@ def test_gpu_fp6_cast_matches_host_on_every_in_range_half():
 @pytest.mark.parametrize("m,k,n,qc,n_total,col4,col6", [
     (16, 512, 512, 128, 2048, 384, 1536 + 128),
     (48, 512, 512, 128, 2048, 384, 1536 + 128),
+    (48, 512, 512, 128, 2048, 388, 1536 + 132),       # up to 128 rows: C leaves as 8-byte stores, these outputs as 2-byte stores
+    (100, 2048, 512, 128, 2048, 384, 1536 + 128),     # 128-row tile, strips shared by two CTAs and reduced by eight groups
+    (100, 2048, 512, 128, 2048, 388, 1536 + 132),
+    (30, 2048, 512, 128, 2048, 388, 1536 + 132),
     (300, 512, 512, 128, 2048, 384, 1536 + 128),      # the kernel for more than 128 rows, 16-byte row stores
     (300, 512, 512, 128, 2048, 388, 1536 + 132),      # column bases off the 16-byte grid: 2-byte stores
     (200, 1024, 1248 + 32, 32, 4096, 1248, 3000),     # ragged strips (9.75 INT4 strips, 32 FP6 columns)
