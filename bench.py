@@ -310,9 +310,10 @@ class LayerBench:
             dist.all_gather_into_tensor(self.gathered, self.c_dev)
 
     def launches_per_step(self):
-        # up to 128 rows: one launch; more: launches of up to min(32, 64 MB / (256 K 2 B)) tiles of 256 rows
-        rows_per_launch = 256 * max(1, min(32, (64 << 20) // (256 * self.k * 2)))
-        per_gemm = 1 if self.m <= 128 else -(-self.m // rows_per_launch)
+        # the library's own launch plan for this shape and device
+        import torch
+        sms = torch.cuda.get_device_properties(self.env["dev"]).multi_processor_count
+        per_gemm, _ = self.env["fm"].launch_plan(self.m, self.n_local, self.k, self.qc_local, sms)
         return per_gemm + (1 if self.exchange is not None else 0)
 
     # ---- timing

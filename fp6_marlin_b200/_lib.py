@@ -33,6 +33,7 @@ SIGNATURES = {
     "fp6m_repack_from_reference": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "fp6m_schedule": (_i, [_i, _i, _i, _i, _i, _vp]),
     "fp6m_mul_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "fp6m_mul_launches": (_i, [_i, _i, _i, _i, _i, _vp]),
     "fp6m_mul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp, _sz, _i, _vp,
                       _i, _i, _i, _i, _i, _i, _i, _vp]),
     "fp6m_mul_fused": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp, _sz, _i, _vp,

@@ -240,6 +240,15 @@ def schedule(k: int, n: int, quant_cols: int = -1, group_size: int = -1, ctas: i
     return list(buf), total
 
 
+def launch_plan(m: int, n: int, k: int, quant_cols: int = -1, sms: int = 148):
+    """How `mul` cuts the shape into kernel launches on a device with `sms` multiprocessors: (number of
+    launches, True if the kernel for more than 128 rows runs)."""
+    import ctypes
+    many = ctypes.c_int(0)
+    launches = lib.fp6m_mul_launches(m, n, k, quant_cols, sms, ctypes.byref(many))
+    return launches, bool(many.value)
+
+
 # ----------------------------------------------------------------------------------------------
 # mul
 # ----------------------------------------------------------------------------------------------

@@ -45,17 +45,27 @@ struct DeviceGuard {
 
 // How a GEMM of M rows is cut into launches: kernel, tile of rows, rows per launch, grid.
 struct LaunchPlan {
-  bool wide;        // more than kTc5MaxRows rows: the kernel with scaled operands and tiles of 128 / 256 rows
+  bool wide;        // the kernel with scaled operands and tiles of 256 rows
   int tile;         // rows of A per MMA tile
   int rows;         // rows of A per launch
   int ctas;         // grid of the first (largest) launch
 };
 
 // `sms` <= 0: the largest grid any device can get (an upper bound for sizing buffers).
-LaunchPlan plan_launches(int M, const Geometry& geo, int sms) {
+LaunchPlan plan_launches(int M, const Geometry& geo, int sms, int two_launches = -1) {
   LaunchPlan lp;
-  lp.wide = M > kTc5MaxRows;
-  lp.tile = lp.wide ? wide_tile_rows(M) : tc5_tile_rows(M);
+  // 129 to 256 rows on a layer with few blocks per CTA: two launches of the kernel for up to 128 rows beat one
+  // 256-row tile of the other kernel, whose split-K partials are 256 KB per CTA and strip.  Measured at 256 / 160
+  // rows: K = N = 8192 (28 blocks per CTA) 59 -> 57 / 58 -> 44 us, 4096 x 4096 46.5 -> 40, 11008 x 4096 59 -> 53,
+  // 4096 x 22016 (37 blocks) 70.5 -> 69.8; K = N = 16384 (111 blocks) is 4 % slower that way, and so are three launches
+  // for 384 rows.  `two_launches`: -1 decides here, 0 / 1 force (sizing a buffer for either).
+  bool two = false;
+  if (M > kTc5MaxRows && M <= 2 * kTc5MaxRows) {
+    const long long blocks = (long long)(geo.strips4 + geo.strips6) * geo.k128;
+    two = two_launches < 0 ? blocks <= 48ll * (sms > 0 ? sms : 148) : two_launches != 0;
+  }
+  lp.wide = M > kTc5MaxRows && !two;
+  lp.tile = lp.wide ? wide_tile_rows(M) : tc5_tile_rows(M < kTc5MaxRows ? M : kTc5MaxRows);
   // CTAs own contiguous ranges of (tile, strip) pairs, so the tiles of a launch are all in flight at once:
   // keep their activations (tile x K halves each) within half of L2
   // (measured at K = 16384: 64 MB of activations per launch are as fast as 32 MB on a full layer and 23 % faster
@@ -101,7 +111,22 @@ size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms) {
     return (b + 255) & ~(size_t)255;
   }
   const int qc = quant_cols < 0 ? 0 : (quant_cols > N ? N : quant_cols);
-  return scratch_bytes_of(plan_launches(M, make_geometry(K, N, qc, 128), sms));
+  const Geometry geo = make_geometry(K, N, qc, 128);
+  if (sms <= 0 && M > kTc5MaxRows && M <= 2 * kTc5MaxRows) {
+    // no device given: enough for either way of cutting 129 to 256 rows into launches
+    const size_t a = scratch_bytes_of(plan_launches(M, geo, sms, 0)), b = scratch_bytes_of(plan_launches(M, geo, sms, 1));
+    return a > b ? a : b;
+  }
+  return scratch_bytes_of(plan_launches(M, geo, sms));
+}
+
+int fp6m_mul_launches(int M, int N, int K, int quant_cols, int sms, int* many_rows_kernel) {
+  if (many_rows_kernel) *many_rows_kernel = 0;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int qc = quant_cols < 0 ? 0 : (quant_cols > N ? N : quant_cols);
+  const LaunchPlan lp = plan_launches(M, make_geometry(K, N, qc, 128), sms);
+  if (many_rows_kernel) *many_rows_kernel = lp.wide ? 1 : 0;
+  return (M + lp.rows - 1) / lp.rows;
 }
 
 }  // extern "C"
@@ -145,8 +170,8 @@ int mul_impl(const void* A, const void* B, void* C, const void* s, int M, int N,
   MulParams p;
   p.geo = make_geometry(K, N, qc, group_size);
   if ((long long)kMaxRowTiles * (p.geo.strips4 + p.geo.strips6) * units_per_strip(p.geo) > 0x3fffffff) return FP6M_ERR_PROB_SHAPE;
-  // up to kTc5MaxRows rows: the kernel with fp32 group scaling; more: the wide kernel, tiles of up to 256 rows,
-  // up to kMaxRowTiles tiles per launch
+  // up to kTc5MaxRows rows (up to twice as many on a small layer, in two launches): the kernel with fp32 group
+  // scaling; more: the wide kernel, tiles of 256 rows, up to kMaxRowTiles tiles per launch
   const LaunchPlan lp = plan_launches(M, p.geo, sms);
   const bool wide = lp.wide;
   const int tile = lp.tile, rows = lp.rows, ctas = lp.ctas;

@@ -507,18 +507,26 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
         float sum[CH];
 #pragma unroll
         for (int i = 0; i < CH; ++i) sum[i] = 0.f;
-        for (int cc = c_lo; cc <= cta; ++cc) {
-          if (p.sched.bound[cc] >= p.sched.bound[cc + 1]) continue;
-          const unsigned long long* src = slot_of(cc, reduce_strip) + m0 * kStripCols;
-          unsigned long long v[CH];
+        // two contributors per round trip to L2 (32 tagged words in flight per thread); added in CTA order
+#pragma unroll 1
+        for (int cc = c_lo; cc <= cta; cc += 2) {
+          // a CTA without work stored nothing; this CTA's own slot (present for sure) stands in for it
+          const bool live0 = p.sched.bound[cc] < p.sched.bound[cc + 1];
+          const bool live1 = cc + 1 <= cta && p.sched.bound[cc + 1] < p.sched.bound[cc + 2];
+          const unsigned long long* src0 = slot_of(live0 ? cc : cta, reduce_strip) + m0 * kStripCols;
+          const unsigned long long* src1 = slot_of(live1 ? cc + 1 : cta, reduce_strip) + m0 * kStripCols;
+          unsigned long long v0[CH], v1[CH];
           bool all_here = false;
 #pragma unroll 1
           for (int spin = 0; spin < (1 << 20) && !all_here; ++spin) {
 #pragma unroll
-            for (int i = 0; i < CH; ++i) v[i] = ld_relaxed_u64(src + i * kStripCols);
+            for (int i = 0; i < CH; ++i) v0[i] = ld_relaxed_u64(src0 + i * kStripCols);
+#pragma unroll
+            for (int i = 0; i < CH; ++i) v1[i] = ld_relaxed_u64(src1 + i * kStripCols);
             all_here = true;
 #pragma unroll
-            for (int i = 0; i < CH; ++i) all_here = all_here && (uint32_t)(v[i] >> 32) == reduce_tag;
+            for (int i = 0; i < CH; ++i)
+              all_here = all_here && (uint32_t)(v0[i] >> 32) == reduce_tag && (uint32_t)(v1[i] >> 32) == reduce_tag;
             if (dead) break;
           }
           if (!all_here && !dead) {
@@ -526,7 +534,10 @@ w46_gemm_wide_kernel(const __grid_constant__ MulParams p, const __grid_constant_
             if (p.status) atomicExch(p.status, kStatusTimeout);
           }
 #pragma unroll
-          for (int i = 0; i < CH; ++i) sum[i] += __uint_as_float((uint32_t)v[i]);
+          for (int i = 0; i < CH; ++i) {
+            sum[i] += live0 ? __uint_as_float((uint32_t)v0[i]) : 0.f;
+            sum[i] += live1 ? __uint_as_float((uint32_t)v1[i]) : 0.f;
+          }
         }
         store_rows(sl, m0, sum, col_scale, writes);
       }

@@ -92,6 +92,11 @@ int fp6m_schedule(int K, int N, int qc, int group_size, int ctas, int* bounds);
  * (it holds per-strip epoch words and tagged split-K slots), or pass a freshly zeroed one. */
 size_t fp6m_mul_scratch_bytes(int M, int N, int K, int quant_cols, int sms);
 
+/* How fp6m_mul cuts this shape into kernel launches on a device with `sms` multiprocessors (the reference's
+ * dispatcher likewise covers M in several launches, fp6_marlin_cuda_kernel.cu:917-948): returns their number;
+ * *many_rows_kernel (may be null) = 1 if the kernel for more than 128 rows runs, 0 if the one for up to 128. */
+int fp6m_mul_launches(int M, int N, int K, int quant_cols, int sms, int* many_rows_kernel);
+
 /* C[M,N] (fp16, row-major, overwritten) = A[M,K] (fp16, row-major) x dequant(B, s).
  * Stands in for fp6_marlin_cuda(...) (fp6_marlin/fp6_marlin_cuda_kernel.cu:864-951) as called from
  * fp6_marlin_mul (fp6_marlin/fp6_marlin_cuda.cpp:47-92): same pointer roles, same tuning

@@ -69,6 +69,27 @@ def test_compute_bound_geometry_with_several_launches(qc):
         assert err <= TOL, (qc, m, err)
 
 
+def test_one_ragged_256_row_tile_on_a_large_layer():
+    """129 to 256 rows run in the kernel for more than 128 rows only on a layer with many blocks per CTA (on a
+    smaller one two launches of the other kernel are faster): K = 16384, N = 7424 has 58 x 128 blocks.  Checked on
+    four strips of columns (first, middle and last INT4 strip, the FP6 strips) against the oracle."""
+    dev = _dev()
+    k, n, qc, gs = 16384, 7424, 256, 128
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    w = synth.make_weight_fp16(k, n, qc, seed=77)
+    ww = fm.make_w46_weight(w, qc, gs, keep_dequantized=False, quant_device=dev)
+    cols = np.r_[0:128, 3712:3840, 7040:7168, 7168:7424]
+    w_deq = _oracle_weight(w[:, cols], qc, gs)
+    for m in (130, 200, 256):
+        assert fm.launch_plan(m, n, k, qc, sms) == (1, True)
+        a = synth.make_activations(m, k, seed=m)
+        c = _mul(a.to(dev), ww, m, n, qc, gs, dev).cpu().numpy().astype(np.float32)
+        err = F.rel_frobenius(c[:, cols], F.gemm_reference(a.numpy(), w_deq))
+        assert err <= TOL, (m, err)
+    assert fm.launch_plan(200, 8192, 8192, 256, sms) == (2, False)      # few blocks per CTA: two launches of 128 rows
+    assert fm.launch_plan(300, 8192, 8192, 256, sms) == (1, True)
+
+
 def _all_codes_problem(k, n4, n6, gs, seed):
     """Codes chosen so that every INT4 code and every FP6 code occurs at every row position of a 128-row
     block (checked), random fp16 scales; returns packed tensors and the oracle's dequantised weights."""
@@ -92,10 +113,11 @@ def _all_codes_problem(k, n4, n6, gs, seed):
 
 
 @pytest.mark.parametrize("gs", [128, -1])
-@pytest.mark.parametrize("m", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("m", [16, 32, 64, 128, 256, 512])
 def test_every_code_in_every_position_through_the_gemm(m, gs):
-    """One-hot rows of A make every output a single product: the kernel for up to 16 rows (m = 16) and every
-    tile width of the kernel for more rows must return the oracle's dequantised weights bit for bit."""
+    """One-hot rows of A make every output a single product: every instance of the kernel for up to 128 rows
+    (m = 256: two launches of it) and the kernel for more rows (m = 512) must return the oracle's dequantised
+    weights bit for bit."""
     dev = _dev()
     k, n4, n6 = 1024, 384, 128
     n = n4 + n6
