@@ -94,7 +94,10 @@ struct Tc5Cfg {
   // the first two teams where there are only two sets.  Eight (128-row tiles, where a strip's partials are 128 KB
   // per contributor and the reduction is a chain of round trips to L2): the four sets, the two teams and the
   // eight warps in front of them (producers, issuers, two spare warps), sixteen rows each.
-  // (measured at 128 rows, K = N = 8192: 32.0 -> 27.7 us per GEMM; K = N = 4096: 26.0 -> 19.9)
+  // (measured at 128 rows, K = N = 8192: 32.0 -> 27.7 us per GEMM; K = N = 4096: 26.0 -> 19.9.  Unequal shares -
+  // fewer rows for the epilogue sets, which get there last - measured: 128 rows, sets x 8 + the others x 24: 30.0 us;
+  // 64 rows, sets x 8 + teams and front warps x 12: the same as four groups; 32 rows, sets x 4 + three teams x 8:
+  // -1.7 %, but the 16-row instance compiled from that source ran 0.7 % slower.)
   static constexpr int kReduceGroups = (kEpiSets == 4 && kTeams == 2 && kDeqBase == 8) ? 8 : 4;
   static_assert(kTeams >= 2 && STAGES_ <= 4 * kTeams + 4 * kEpiSets, "the first round of weight copies is issued by one warp per stage");
   static constexpr int kEpochWarp = 2 + kIssuers - 1;
