@@ -272,3 +272,27 @@ def test_w46_linear_bookkeeping():
     nwords, nscales = fm.b200_sizes(in_f, out_f, qc, 128)
     assert layer.B.numel() == nwords and layer.s.numel() == nscales
     assert "fp6_columns=256" in repr(layer)
+
+
+def test_launch_plan_and_scratch_sizes():
+    """How the host cuts M rows into launches (the reference's dispatcher loops over batches of rows as well,
+    fp6_marlin_cuda_kernel.cu:917-948): one launch of the kernel for up to 128 rows; 129 to 256 rows as two launches
+    of it on a layer with at most 48 blocks per CTA, else one 256-row tile of the other kernel; more rows in launches
+    whose activations stay within 64 MB.  The scratch size asked for without a device covers either plan."""
+    sms = 148
+    assert fm.launch_plan(0, 8192, 8192, 256, sms) == (0, False)
+    for m in (1, 16, 17, 64, 128):
+        assert fm.launch_plan(m, 8192, 8192, 256, sms) == (1, False)
+    for m in (129, 200, 256):
+        assert fm.launch_plan(m, 8192, 8192, 256, sms) == (2, False)        # 64 strips x 64 blocks = 28 per CTA
+        assert fm.launch_plan(m, 16384, 16384, 256, sms) == (1, True)       # 128 x 128 blocks = 111 per CTA
+    assert fm.launch_plan(257, 8192, 8192, 256, sms) == (1, True)
+    assert fm.launch_plan(8192, 8192, 8192, 256, sms) == (2, True)          # 16 tiles of 256 rows x 16 KB per row = 64 MB
+    assert fm.launch_plan(8192, 16384, 16384, 256, sms) == (4, True)        # K = 16384: eight tiles per launch
+    assert fm.launch_plan(8192, 2048, 16384, 32, sms) == (4, True)
+    need = _lib.lib.fp6m_mul_scratch_bytes
+    for shape in ((200, 8192, 8192, 256), (200, 16384, 16384, 256), (256, 4096, 4096, -1)):
+        assert need(*shape, -1) >= need(*shape, sms)
+        assert need(*shape, -1) >= need(*shape, 8)                           # a device with few SMs takes the other plan
+    assert need(0, 0, 0, 0, -1) >= need(8192, 16384, 16384, 256, sms)
+    assert need(128, 8192, 8192, 256, sms) >= need(16, 8192, 8192, 256, sms)
