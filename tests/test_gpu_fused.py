@@ -26,7 +26,7 @@ def _oracle_weight(w: torch.Tensor, qc: int, gs: int) -> np.ndarray:
     return np.concatenate(parts, axis=1)
 
 
-@pytest.mark.parametrize("m", [1, 16, 48, 300])
+@pytest.mark.parametrize("m", [1, 16, 48, 200, 300])      # 200 rows: two launches of the kernel for up to 128 rows
 @pytest.mark.parametrize("k,inter,qc,gs", [(1024, 1408, 256, 128), (512, 640, 64, -1), (2048, 512, 0, 128)])
 def test_gate_up_activation_in_the_epilogue(m, k, inter, qc, gs):
     dev = torch.device("cuda:0")
@@ -52,7 +52,7 @@ def test_gate_up_activation_in_the_epilogue(m, k, inter, qc, gs):
     assert err <= TOL, (m, k, inter, qc, gs, err)
 
 
-@pytest.mark.parametrize("m", [1, 16, 100])
+@pytest.mark.parametrize("m", [1, 16, 100, 200])
 def test_residual_add_in_the_epilogue(m):
     dev = torch.device("cuda:0")
     k, n, qc, gs = 2048, 1024, 256, 128
